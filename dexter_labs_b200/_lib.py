@@ -1,0 +1,60 @@
+"""ctypes binding of ``libdexter_b200.so`` (declarations: ``include/dexter_b200.h``).
+
+There is no fallback: if the library is missing the import fails with the build
+command, and no op in this package computes anything without it.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libdexter_b200.so"
+
+OK = 0
+ERRORS = {
+    -1: "DXB_ERR_BITS", -2: "DXB_ERR_NULL", -3: "DXB_ERR_SHAPE", -4: "DXB_ERR_UNSUPPORTED",
+    -5: "DXB_ERR_WORKSPACE", -6: "DXB_ERR_TENSORMAP", -7: "DXB_ERR_CUDA",
+    -8: "DXB_ERR_KERNEL_TIMEOUT",
+}
+
+# name -> (restype, argtypes); one entry per symbol declared in include/dexter_b200.h
+SIGNATURES = {
+    "dxb_wq_gemm": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
+                            c_int, c_void_p]),
+    "dxb_w4a16": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_int64, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "dxb_w8a16": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_int64, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "dxb_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "dxb_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                               c_void_p]),
+    "dxb_uses_tensor_cores": (c_int, [c_int, c_int, c_int, c_int, c_int]),
+    "dxb_read_status": (c_int, [c_void_p, c_void_p]),
+    "dxb_strerror": (c_char_p, [c_int]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once; raise loudly when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m dexter_labs_b200.build` "
+            "(needs nvcc; there is no non-CUDA fallback)")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means header and library disagree
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def strerror(code: int) -> str:
+    return load().dxb_strerror(code).decode()

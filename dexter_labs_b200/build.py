@@ -1,0 +1,58 @@
+"""In-tree build of the CUDA library (``libdexter_b200.so``) for sm_100a.
+
+``python -m dexter_labs_b200.build`` (or :func:`build`) runs nvcc on
+``csrc/wq_gemm.cu`` and leaves the shared library next to this file, where
+:mod:`dexter_labs_b200._lib` loads it.  nvcc cross-compiles without a GPU.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+SOURCES = [PKG_DIR / "csrc" / "wq_gemm.cu"]
+HEADERS = [PKG_DIR / "csrc" / "sm100_ptx.cuh", PKG_DIR.parent / "include" / "dexter_b200.h"]
+LIB_PATH = PKG_DIR / "libdexter_b200.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    "-shared", "-Xcompiler", "-fPIC",
+]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found; set NVCC or put it on PATH")
+
+
+def is_stale() -> bool:
+    if not LIB_PATH.exists():
+        return True
+    built = LIB_PATH.stat().st_mtime
+    return any(src.stat().st_mtime > built for src in SOURCES + HEADERS if src.exists())
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile the library if it is missing or older than its sources."""
+    if not force and not is_stale():
+        return LIB_PATH
+    cmd = [_nvcc(), *NVCC_FLAGS]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += ["-o", str(LIB_PATH), *[str(s) for s in SOURCES]]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or proc.returncode:
+        sys.stderr.write(proc.stdout + proc.stderr)
+    if proc.returncode:
+        raise RuntimeError(f"nvcc failed ({proc.returncode}): {' '.join(cmd)}")
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

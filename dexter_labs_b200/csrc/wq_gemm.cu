@@ -1,0 +1,885 @@
+// Weight-only quantised GEMM for sm_100a:  Y[M,N] = X[M,K] @ dequant(Q)[K,N] (+ bias)
+//
+//   Q       packed weights exactly as the reference quantiser lays them out
+//           (python/dexter/quant.py:62-133): int4 = [K/2, N] bytes, low nibble is
+//           row i, high nibble is row i + K/2 ("split-half"); int8 = [K, N] bytes.
+//   scales  [K/G, N] bf16, zeros [K/G, N] bf16 or absent (symmetric).
+//   W[k,n]  = bf16( (q - zero) * scale ), one rounding, bit-identical to the
+//           reference's torch dequantize (python/dexter/ops/reference/gemm.py:51-73).
+//   Y       = bf16( sum_k X*W in fp32 ), then bf16( Y + bias ) as a second rounding,
+//           as the reference does (gemm.py:76-79).
+//
+// Tensor-core kernel (wq_gemm_tc): the weight tile is the 128-row UMMA "M"
+// operand and the tokens are the UMMA "N" (swap-AB), so M = 83 tokens costs a
+// 96-wide MMA instead of a 128-row one.  Per CTA, per unit of 64 packed rows x
+// 128 columns:
+//   warp 0      TMA producer: packed bytes (+ scale / zero rows) and the matching
+//               X k-slices land in a shared-memory ring (128 B swizzle).
+//   warps 6-13  dequantise: ld.shared of packed words, nibble -> bf16 by bit
+//               pattern (OR into 0x4300 = 128.0, exact subtract, one multiply; no
+//               int->float convert), k-pairs formed with two byte permutes, and
+//               written straight into TMEM with tcgen05.st.16x128b (the dequantised
+//               tile never touches shared memory).
+//   warp 1      one thread issues tcgen05.mma (A = weights from TMEM, B = X from
+//               shared memory, fp32 accumulators in TMEM).
+//   warps 2-5   epilogue: tcgen05.ld, bias, bf16 stores; or fp32 partials.
+// Work is split stream-K style: the (tile, unit) space is cut into equal contiguous
+// ranges, one per CTA; a tile shared by several CTAs is finished by whichever CTA
+// arrives last (no CTA ever waits for another one), summing the partials in a
+// fixed order so results are deterministic.
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/dexter_b200.h"
+#include "sm100_ptx.cuh"
+
+namespace dx {
+
+// ------------------------------------------------------------------ constants
+constexpr int kTileN = 128;      // weight columns per tile (UMMA M)
+constexpr int kUnitRows = 64;    // packed rows per pipeline unit
+constexpr int kQBytes = kTileN * kUnitRows;  // 8192
+constexpr int kWStage = kQBytes + 1024;      // + 2 scale rows + 2 zero rows of 256 B
+constexpr int kMaxStages = 8;
+constexpr int kAStages = 4;      // dequantised-tile ring in TMEM
+constexpr int kACol0 = 256;      // TMEM column where that ring starts
+constexpr int kThreads = 448;    // 14 warps
+constexpr int kDequantThreads = 256;
+constexpr int kEpilogueThreads = 128;
+constexpr int kSmemBudget = 227 * 1024 - 4096;
+constexpr int kMaxTiles = 16384;  // tile counters reserved in every workspace
+
+struct WqParams {
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* out;
+  long long ldo;
+  float* partials;
+  int* counters;
+  int* status;
+  int M, N, K, group;
+  int NU;              // tokens padded to a multiple of 16: the UMMA N
+  int units_per_tile;  // packed rows / 64
+  int tiles;           // ceil(N / 128)
+  int total_units;
+  int half_k;          // int4: K/2 (first activation column of the high-nibble plane)
+  int stages;
+  int x_stage_bytes;   // planes * NU * 128
+  int max_slots;       // partial slots reserved per tile
+  int nacc;            // accumulator buffers in TMEM (2 when NU <= 128)
+};
+
+struct alignas(8) Barriers {
+  uint64_t full_w[kMaxStages], empty_w[kMaxStages];
+  uint64_t full_x[kMaxStages], empty_x[kMaxStages];
+  uint64_t a_full[kAStages], a_empty[kAStages];
+  uint64_t acc_full[2], acc_empty[2];
+};
+
+// -------------------------------------------------------------- dequant math
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+__device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t cvt_bf16x2(float hi, float lo) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+// Two nibbles (bits 0..3 and 16..19 of `w`) -> two bf16 weights.  OR-ing a nibble
+// into the mantissa of 0x4300 gives 128 + q exactly; `zero2` holds 128 + zero
+// point in both halves (0x4308 = 136.0 for the symmetric midpoint 8), so the
+// subtract is exact and the multiply is the only rounding.
+__device__ __forceinline__ uint32_t deq4(uint32_t w, uint32_t zero2, uint32_t scale2) {
+  const uint32_t v = (w & 0x000F000Fu) | 0x43004300u;
+  return mul_bf16x2(sub_bf16x2(v, zero2), scale2);
+}
+// One byte -> fp32 by bit pattern: 0x4B0000qq = 8388608 + q.  `cz` = 8388608 +
+// zero point; subtract and multiply are both exact in fp32 (8-bit x 8-bit
+// significands), so the later cvt.rn to bf16 is the only rounding.
+__device__ __forceinline__ float deq8(uint32_t word, uint32_t byte_sel, float cz, float scale) {
+  const float f = __uint_as_float(prmt(word, 0x4B000000u, 0x7650u + byte_sel));
+  return (f - cz) * scale;
+}
+__device__ __forceinline__ uint32_t dup_lo(uint32_t w) { return prmt(w, w, 0x1010u); }
+__device__ __forceinline__ uint32_t dup_hi(uint32_t w) { return prmt(w, w, 0x3232u); }
+__device__ __forceinline__ float bf16lo_f32(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi_f32(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// First unit of CTA c and the CTA that owns unit u, for `total` units cut into
+// `ctas` contiguous ranges.
+__host__ __device__ inline long long range_begin(long long c, long long total, long long ctas) {
+  return c * total / ctas;
+}
+__host__ __device__ inline int owner_of(long long u, long long total, long long ctas) {
+  return static_cast<int>(((u + 1) * ctas - 1) / total);
+}
+
+// ----------------------------------------------------------------- the kernel
+template <int BITS, bool HAS_ZERO>
+__global__ void __launch_bounds__(kThreads, 1)
+wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_x,
+           const __grid_constant__ CUtensorMap tm_s, const __grid_constant__ CUtensorMap tm_z,
+           const WqParams p) {
+  constexpr int PLANES = BITS == 4 ? 2 : 1;
+  constexpr int A_STAGE_COLS = PLANES * 32;
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ Barriers bars;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  __shared__ int last_flag;
+
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t w_ring = smem0;
+  const uint32_t x_ring = smem0 + p.stages * kWStage;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int S = p.stages;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    last_flag = 0;
+    for (int s = 0; s < kMaxStages; ++s) {
+      mbar_init(smem_u32(&bars.full_w[s]), 1);
+      mbar_init(smem_u32(&bars.empty_w[s]), kDequantThreads);
+      mbar_init(smem_u32(&bars.full_x[s]), 1);
+      mbar_init(smem_u32(&bars.empty_x[s]), 1);
+    }
+    for (int t = 0; t < kAStages; ++t) {
+      mbar_init(smem_u32(&bars.a_full[t]), kDequantThreads);
+      mbar_init(smem_u32(&bars.a_empty[t]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bars.acc_full[b]), 1);
+      mbar_init(smem_u32(&bars.acc_empty[b]), kEpilogueThreads);
+    }
+    mbar_init_fence();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_s);
+    if (HAS_ZERO) tma_prefetch_desc(&tm_z);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem0 = tmem_base_s;
+
+  // This CTA's contiguous range of (tile, unit) work.
+  const long long TU = p.total_units;
+  const long long G = gridDim.x;
+  const long long u_begin = range_begin(blockIdx.x, TU, G);
+  const long long u_end = range_begin(blockIdx.x + 1, TU, G);
+  const int U = p.units_per_tile;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ===================================================== TMA producer ====
+    if (lane == 0) {
+      const uint32_t w_bytes = kQBytes + PLANES * 256 * (HAS_ZERO ? 2 : 1);
+      const uint32_t x_bytes = p.x_stage_bytes;
+      long long it = 0;
+      bool ok = true;
+      for (long long u = u_begin; u < u_end && ok; ++u, ++it) {
+        const int tile = static_cast<int>(u / U);
+        const int ku = static_cast<int>(u % U);
+        const int s = static_cast<int>(it % S);
+        const uint32_t ph = static_cast<uint32_t>(it / S) & 1u;
+        ok = mbar_wait(smem_u32(&bars.empty_w[s]), ph ^ 1u, abortp) &&
+             mbar_wait(smem_u32(&bars.empty_x[s]), ph ^ 1u, abortp);
+        if (!ok) break;
+        const uint32_t wdst = w_ring + s * kWStage;
+        const uint32_t xdst = x_ring + s * p.x_stage_bytes;
+        const uint32_t fw = smem_u32(&bars.full_w[s]);
+        const uint32_t fx = smem_u32(&bars.full_x[s]);
+        const int n0 = tile * kTileN;
+        const int r0 = ku * kUnitRows;
+        mbar_expect_tx(fw, w_bytes);
+        tma_load_2d(wdst, &tm_q, fw, n0, r0);
+#pragma unroll
+        for (int pl = 0; pl < PLANES; ++pl) {
+          const int k0 = r0 + pl * p.half_k;
+          const int g = k0 / p.group;
+          tma_load_2d(wdst + kQBytes + pl * 256, &tm_s, fw, n0, g);
+          if (HAS_ZERO) tma_load_2d(wdst + kQBytes + 512 + pl * 256, &tm_z, fw, n0, g);
+        }
+        mbar_expect_tx(fx, x_bytes);
+#pragma unroll
+        for (int pl = 0; pl < PLANES; ++pl)
+          tma_load_2d(xdst + pl * p.NU * 128, &tm_x, fx, r0 + pl * p.half_k, 0);
+      }
+      if (!ok) {
+        // Leaving early: let the copies already issued land before the CTA exits.
+        for (long long j = (it > S ? it - S : 0); j < it; ++j) {
+          const int s = static_cast<int>(j % S);
+          const uint32_t ph = static_cast<uint32_t>(j / S) & 1u;
+          for (int spin = 0; spin < 200000; ++spin)
+            if (mbar_try_wait(smem_u32(&bars.full_w[s]), ph) &&
+                mbar_try_wait(smem_u32(&bars.full_x[s]), ph))
+              break;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ======================================================= MMA issuer ====
+    if (lane == 0) {
+      const uint32_t idesc = idesc_bf16_f32(kTileN, p.NU);
+      const uint64_t xdesc0 = smem_desc_kmajor_sw128(x_ring);
+      const uint32_t x_stage16 = static_cast<uint32_t>(p.x_stage_bytes) >> 4;
+      const uint32_t plane16 = static_cast<uint32_t>(p.NU * 128) >> 4;
+      long long it = 0;
+      int seg = 0;
+      bool ok = true;
+      long long u = u_begin;
+      while (u < u_end && ok) {
+        const int ku0 = static_cast<int>(u % U);
+        const long long left = u_end - u;
+        const int nun = static_cast<int>(left < (U - ku0) ? left : (U - ku0));
+        const int b = seg % p.nacc;
+        const uint32_t accph = static_cast<uint32_t>(seg / p.nacc) & 1u;
+        ok = mbar_wait(smem_u32(&bars.acc_empty[b]), accph ^ 1u, abortp);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem0 + b * p.NU;
+        for (int i = 0; i < nun; ++i, ++it) {
+          const int s = static_cast<int>(it % S);
+          const uint32_t ph = static_cast<uint32_t>(it / S) & 1u;
+          const int t = static_cast<int>(it % kAStages);
+          const uint32_t aph = static_cast<uint32_t>(it / kAStages) & 1u;
+          ok = mbar_wait(smem_u32(&bars.full_x[s]), ph, abortp) &&
+               mbar_wait(smem_u32(&bars.a_full[t]), aph, abortp);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t xd = xdesc0 + static_cast<uint64_t>(s * x_stage16);
+          const uint32_t a_tmem = tmem0 + kACol0 + t * A_STAGE_COLS;
+#pragma unroll
+          for (int pl = 0; pl < PLANES; ++pl) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              mma_ts(d_tmem, a_tmem + pl * 32 + kk * 8, xd + pl * plane16 + kk * 2, idesc,
+                     (i | pl | kk) != 0);
+            }
+          }
+          tc_commit(smem_u32(&bars.a_empty[t]));
+          tc_commit(smem_u32(&bars.empty_x[s]));
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&bars.acc_full[b]));
+        u += nun;
+        ++seg;
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ========================================================= epilogue ====
+    const int q = warp & 3;                       // this warp's TMEM lane quadrant
+    const int etid = (warp - 2) * 32 + lane;      // 0..127 within the epilogue group
+    // TMEM lane -> weight column inside the tile (see the dequant mapping below).
+    const int n_local = 32 * q + 4 * (lane & 7) + (lane >> 3);
+    int seg = 0;
+    bool ok = true;
+    long long u = u_begin;
+    while (u < u_end && ok) {
+      const int tile = static_cast<int>(u / U);
+      const int ku0 = static_cast<int>(u % U);
+      const long long left = u_end - u;
+      const int nun = static_cast<int>(left < (U - ku0) ? left : (U - ku0));
+      const bool whole = (nun == U);
+      const int b = seg % p.nacc;
+      const uint32_t accph = static_cast<uint32_t>(seg / p.nacc) & 1u;
+      ok = mbar_wait(smem_u32(&bars.acc_full[b]), accph, abortp);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_addr(tmem0 + b * p.NU, 32 * q, 0);
+      const int n = tile * kTileN + n_local;
+      if (whole) {
+        const float bias = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
+        const bool has_bias = p.bias != nullptr;
+        for (int c0 = 0; c0 < p.NU; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld_32x32b_x16(d_tmem + c0, v);
+          tc_wait_ld();
+          if (n < p.N) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const int m = c0 + c;
+              if (m < p.M) {
+                __nv_bfloat16 o = __float2bfloat16_rn(__uint_as_float(v[c]));
+                if (has_bias) o = __float2bfloat16_rn(__bfloat162float(o) + bias);
+                p.out[static_cast<long long>(m) * p.ldo + n] = o;
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&bars.acc_empty[b]));
+      } else {
+        // Partial tile: park the fp32 sums, then whoever completes the tile reduces.
+        const int c_first = owner_of(static_cast<long long>(tile) * U, TU, G);
+        const int c_last = owner_of(static_cast<long long>(tile) * U + U - 1, TU, G);
+        const int slot = static_cast<int>(blockIdx.x) - c_first;
+        float* ws = p.partials +
+                    (static_cast<long long>(tile) * p.max_slots + slot) * p.NU * kTileN;
+        for (int c0 = 0; c0 < p.NU; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld_32x32b_x16(d_tmem + c0, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const int m = c0 + c;
+            if (m < p.M) ws[m * kTileN + n_local] = __uint_as_float(v[c]);
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&bars.acc_empty[b]));
+        __threadfence();
+        named_bar_sync(1, kEpilogueThreads);
+        if (etid == 0) {
+          const int old = atomicAdd(&p.counters[tile], nun);
+          const int last = (old + nun == U) ? 1 : 0;
+          if (last) p.counters[tile] = 0;  // ready for the next launch / graph replay
+          __threadfence();
+          last_flag = last;
+        }
+        named_bar_sync(1, kEpilogueThreads);
+        if (last_flag) {
+          const int nslots = c_last - c_first + 1;
+          const int nn = tile * kTileN + etid;
+          const float* base =
+              p.partials + static_cast<long long>(tile) * p.max_slots * p.NU * kTileN + etid;
+          if (nn < p.N) {
+            const bool has_bias = p.bias != nullptr;
+            const float bias = has_bias ? __bfloat162float(p.bias[nn]) : 0.0f;
+            for (int m = 0; m < p.M; ++m) {
+              float acc = 0.0f;
+              for (int sl = 0; sl < nslots; ++sl)
+                acc += __ldcg(base + (static_cast<long long>(sl) * p.NU + m) * kTileN);
+              __nv_bfloat16 o = __float2bfloat16_rn(acc);
+              if (has_bias) o = __float2bfloat16_rn(__bfloat162float(o) + bias);
+              p.out[static_cast<long long>(m) * p.ldo + nn] = o;
+            }
+          }
+        }
+        named_bar_sync(1, kEpilogueThreads);  // last_flag is reused by the next segment
+      }
+      u += nun;
+      ++seg;
+    }
+  } else {
+    // ========================================================== dequant ====
+    // Thread (c = lane % 4, g = lane / 4) of quadrant q reads, for each slab of 8
+    // packed rows, the 32-bit words at rows 2c and 2c+1, byte columns
+    // 32q + 4g .. +3.  Byte b of the word is weight column 32q + 4g + b and goes to
+    // TMEM lane 32q + 8b + g; rows (2c, 2c+1) form one bf16 pair = TMEM column c of
+    // that slab: exactly the register layout of tcgen05.st.16x128b.
+    const int q = warp & 3;
+    const int rh = (warp - 6) >> 2;  // which 32 of the unit's 64 rows
+    const int c = lane & 3;
+    const int g = lane >> 2;
+    const uint32_t chunk = 2 * q + (g >> 2);
+    const uint32_t row0 = 32 * rh + 2 * c;
+    const uint32_t off0 = row0 * 128 + ((chunk ^ (2 * c)) << 4) + 4 * (g & 3);
+    const uint32_t off1 = (row0 + 1) * 128 + ((chunk ^ (2 * c + 1)) << 4) + 4 * (g & 3);
+    const uint32_t sc_off = kQBytes + (32 * q + 4 * g) * 2;
+    const uint32_t lane_base = 32 * q;
+    long long it = 0;
+    bool ok = true;
+    for (long long u = u_begin; u < u_end && ok; ++u, ++it) {
+      const int s = static_cast<int>(it % S);
+      const uint32_t ph = static_cast<uint32_t>(it / S) & 1u;
+      const int t = static_cast<int>(it % kAStages);
+      const uint32_t aph = static_cast<uint32_t>(it / kAStages) & 1u;
+      ok = mbar_wait(smem_u32(&bars.full_w[s]), ph, abortp);
+      if (!ok) break;
+      const uint32_t wsrc = w_ring + s * kWStage;
+      uint32_t w0[4], w1[4];
+#pragma unroll
+      for (int sl = 0; sl < 4; ++sl) {
+        w0[sl] = lds32(wsrc + off0 + sl * 1024);
+        w1[sl] = lds32(wsrc + off1 + sl * 1024);
+      }
+      uint2 sc[PLANES], zr[PLANES];
+#pragma unroll
+      for (int pl = 0; pl < PLANES; ++pl) {
+        sc[pl] = lds64(wsrc + sc_off + pl * 256);
+        if (HAS_ZERO) zr[pl] = lds64(wsrc + sc_off + 512 + pl * 256);
+      }
+      mbar_arrive(smem_u32(&bars.empty_w[s]));  // packed stage is in registers now
+      ok = mbar_wait(smem_u32(&bars.a_empty[t]), aph ^ 1u, abortp);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t a_tmem = tmem0 + kACol0 + t * A_STAGE_COLS + 16 * rh;
+      if (BITS == 4) {
+#pragma unroll
+        for (int pl = 0; pl < 2; ++pl) {
+          const uint32_t s2[4] = {dup_lo(sc[pl].x), dup_hi(sc[pl].x), dup_lo(sc[pl].y),
+                                  dup_hi(sc[pl].y)};
+          uint32_t z2[4];
+          if (HAS_ZERO) {
+            z2[0] = dup_lo(zr[pl].x); z2[1] = dup_hi(zr[pl].x);
+            z2[2] = dup_lo(zr[pl].y); z2[3] = dup_hi(zr[pl].y);
+          } else {
+            z2[0] = z2[1] = z2[2] = z2[3] = 0x43084308u;  // 128 + 8
+          }
+          uint32_t ra[8], rb[8];
+#pragma unroll
+          for (int sl = 0; sl < 4; ++sl) {
+            const uint32_t P = prmt(w0[sl], w1[sl], 0x5410u) >> (4 * pl);
+            const uint32_t Q = prmt(w0[sl], w1[sl], 0x7632u) >> (4 * pl);
+            ra[2 * sl + 0] = deq4(P, z2[0], s2[0]);
+            ra[2 * sl + 1] = deq4(P >> 8, z2[1], s2[1]);
+            rb[2 * sl + 0] = deq4(Q, z2[2], s2[2]);
+            rb[2 * sl + 1] = deq4(Q >> 8, z2[3], s2[3]);
+          }
+          tmem_st_16x128b_x4(tmem_addr(a_tmem + pl * 32, lane_base, 0), ra);
+          tmem_st_16x128b_x4(tmem_addr(a_tmem + pl * 32, lane_base + 16, 0), rb);
+        }
+      } else {
+        const float sf[4] = {bf16lo_f32(sc[0].x), bf16hi_f32(sc[0].x), bf16lo_f32(sc[0].y),
+                             bf16hi_f32(sc[0].y)};
+        float cz[4];
+        if (HAS_ZERO) {
+          cz[0] = 8388608.0f + bf16lo_f32(zr[0].x); cz[1] = 8388608.0f + bf16hi_f32(zr[0].x);
+          cz[2] = 8388608.0f + bf16lo_f32(zr[0].y); cz[3] = 8388608.0f + bf16hi_f32(zr[0].y);
+        } else {
+          cz[0] = cz[1] = cz[2] = cz[3] = 8388608.0f + 128.0f;
+        }
+        uint32_t ra[8], rb[8];
+#pragma unroll
+        for (int sl = 0; sl < 4; ++sl) {
+          ra[2 * sl + 0] = cvt_bf16x2(deq8(w1[sl], 0, cz[0], sf[0]), deq8(w0[sl], 0, cz[0], sf[0]));
+          ra[2 * sl + 1] = cvt_bf16x2(deq8(w1[sl], 1, cz[1], sf[1]), deq8(w0[sl], 1, cz[1], sf[1]));
+          rb[2 * sl + 0] = cvt_bf16x2(deq8(w1[sl], 2, cz[2], sf[2]), deq8(w0[sl], 2, cz[2], sf[2]));
+          rb[2 * sl + 1] = cvt_bf16x2(deq8(w1[sl], 3, cz[3], sf[3]), deq8(w0[sl], 3, cz[3], sf[3]));
+        }
+        tmem_st_16x128b_x4(tmem_addr(a_tmem, lane_base, 0), ra);
+        tmem_st_16x128b_x4(tmem_addr(a_tmem, lane_base + 16, 0), rb);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars.a_full[t]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem0, 512);
+  if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, DXB_ERR_KERNEL_TIMEOUT);
+}
+
+// --------------------------------------------- dense dequantised weight dump
+// W[k,n] bf16 with the same bit-pattern arithmetic as the tensor-core kernel;
+// used to check the dequantisation bit for bit against the reference.
+template <int BITS>
+__global__ void wq_dequant_kernel(const uint8_t* __restrict__ qw, const __nv_bfloat16* __restrict__ scales,
+                                  const __nv_bfloat16* __restrict__ zeros, __nv_bfloat16* __restrict__ out,
+                                  int N, int K, int group) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long total = static_cast<long long>(K) * N;
+  if (idx >= total) return;
+  const int k = static_cast<int>(idx / N);
+  const int n = static_cast<int>(idx % N);
+  const int gi = k / group;
+  const uint32_t sbits = __bfloat16_as_ushort(scales[static_cast<long long>(gi) * N + n]);
+  if (BITS == 4) {
+    const int half = K / 2;
+    const uint32_t byte = k < half ? qw[static_cast<long long>(k) * N + n]
+                                   : (qw[static_cast<long long>(k - half) * N + n] >> 4);
+    const uint32_t z = zeros ? __bfloat16_as_ushort(zeros[static_cast<long long>(gi) * N + n]) : 0x4308u;
+    const uint32_t r = deq4(byte, z | (z << 16), sbits | (sbits << 16));
+    out[idx] = __ushort_as_bfloat16(static_cast<unsigned short>(r & 0xFFFFu));
+  } else {
+    const uint32_t byte = qw[idx];
+    const float cz = 8388608.0f + (zeros ? __bfloat162float(zeros[static_cast<long long>(gi) * N + n]) : 128.0f);
+    const float v = deq8(byte, 0, cz, __uint_as_float(sbits << 16));
+    out[idx] = __ushort_as_bfloat16(static_cast<unsigned short>(cvt_bf16x2(0.0f, v) & 0xFFFFu));
+  }
+}
+
+// ------------------------------------------------------ any-shape CUDA path
+// Plain CUDA-core kernel for shapes the tensor-core kernel does not take (N not
+// a multiple of 16, groups that are not a multiple of 64 rows, K/2 not a multiple
+// of 64).  One thread per output column, 8 tokens per block row; slow but exact
+// in the same sense (bit-identical W, fp32 accumulation).
+template <int BITS>
+__global__ void wq_gemm_simt(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t* __restrict__ qw,
+                             const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ zeros,
+                             const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, long long ldo,
+                             int M, int N, int K, int group) {
+  constexpr int MT = 8;
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int m0 = blockIdx.y * MT;
+  if (n >= N) return;
+  float acc[MT];
+#pragma unroll
+  for (int i = 0; i < MT; ++i) acc[i] = 0.0f;
+  const int half = K / 2;
+  for (int k = 0; k < K; ++k) {
+    const int gi = k / group;
+    const uint32_t sbits = __bfloat16_as_ushort(scales[static_cast<long long>(gi) * N + n]);
+    float w;
+    if (BITS == 4) {
+      const uint32_t byte = k < half ? qw[static_cast<long long>(k) * N + n]
+                                     : (qw[static_cast<long long>(k - half) * N + n] >> 4);
+      const uint32_t z = zeros ? __bfloat16_as_ushort(zeros[static_cast<long long>(gi) * N + n]) : 0x4308u;
+      w = __uint_as_float(deq4(byte, z | (z << 16), sbits | (sbits << 16)) << 16);
+    } else {
+      const float cz = 8388608.0f + (zeros ? __bfloat162float(zeros[static_cast<long long>(gi) * N + n]) : 128.0f);
+      const float v = deq8(qw[static_cast<long long>(k) * N + n], 0, cz, __uint_as_float(sbits << 16));
+      w = __uint_as_float((cvt_bf16x2(0.0f, v) & 0xFFFFu) << 16);
+    }
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+      if (m0 + i < M) acc[i] += __bfloat162float(x[static_cast<long long>(m0 + i) * ldx + k]) * w;
+  }
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+    if (m0 + i < M) {
+      __nv_bfloat16 o = __float2bfloat16_rn(acc[i]);
+      if (bias) o = __float2bfloat16_rn(__bfloat162float(o) + __bfloat162float(bias[n]));
+      out[static_cast<long long>(m0 + i) * ldo + n] = o;
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+static bool make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, uint64_t inner,
+                     uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner,
+                     uint32_t box_outer, CUtensorMapSwizzle sw) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t es[2] = {1, 1};
+  return fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct DeviceInfo {
+  int sms = 0;
+  bool attr_set = false;
+};
+static DeviceInfo& device_info() {
+  static std::mutex mu;
+  static std::unordered_map<int, DeviceInfo> infos;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mu);
+  DeviceInfo& d = infos[dev];
+  if (d.sms == 0) cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
+  return d;
+}
+
+struct Plan {
+  int NU, planes, rows, units_per_tile, tiles, total_units, stages, x_stage_bytes, ctas, max_slots,
+      nacc;
+  size_t smem_bytes;
+};
+
+// Shapes the tensor-core kernel takes.  Everything else goes to wq_gemm_simt.
+static bool tc_supported(int M, int N, int K, int group, int bits) {
+  if (M < 1 || M > 256) return false;
+  if (N % 16 || N < 16) return false;
+  const int rows = bits == 4 ? K / 2 : K;
+  if (bits == 4 && (K % 2)) return false;
+  if (rows % kUnitRows) return false;
+  if (group % kUnitRows || K % group) return false;
+  if (K / group < 1) return false;
+  if ((N + kTileN - 1) / kTileN > kMaxTiles) return false;
+  return true;
+}
+
+static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
+  Plan pl{};
+  pl.NU = ((M + 15) / 16) * 16;
+  pl.planes = bits == 4 ? 2 : 1;
+  pl.rows = bits == 4 ? K / 2 : K;
+  pl.units_per_tile = pl.rows / kUnitRows;
+  pl.tiles = (N + kTileN - 1) / kTileN;
+  pl.total_units = pl.units_per_tile * pl.tiles;
+  pl.x_stage_bytes = pl.planes * pl.NU * 128;
+  int stages = kSmemBudget / (kWStage + pl.x_stage_bytes);
+  pl.stages = stages > kMaxStages ? kMaxStages : stages;
+  pl.smem_bytes = static_cast<size_t>(pl.stages) * (kWStage + pl.x_stage_bytes) + 1024;
+  int ctas = sms;
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  if (ctas > pl.total_units) ctas = pl.total_units;
+  pl.ctas = ctas;
+  pl.nacc = pl.NU <= 128 ? 2 : 1;
+  int max_slots = 1;
+  for (int t = 0; t < pl.tiles; ++t) {
+    const long long u0 = static_cast<long long>(t) * pl.units_per_tile;
+    const int c0 = owner_of(u0, pl.total_units, ctas);
+    const int c1 = owner_of(u0 + pl.units_per_tile - 1, pl.total_units, ctas);
+    if (c1 - c0 + 1 > max_slots) max_slots = c1 - c0 + 1;
+  }
+  pl.max_slots = max_slots;
+  return pl;
+}
+
+constexpr size_t kStatusBytes = 256;
+// The counter block has one fixed size so that calls with different tile counts
+// never let one call's partial sums land on another call's counters.
+static size_t counters_bytes(int) { return static_cast<size_t>(kMaxTiles) * 4; }
+
+template <int BITS, bool HAS_ZERO>
+static int launch_tc(const void* x, long long ldx, const void* qw, const void* scales,
+                     const void* zeros, const void* bias, void* out, long long ldo, int M, int N,
+                     int K, int group, void* workspace, size_t workspace_bytes, int max_ctas,
+                     cudaStream_t stream) {
+  DeviceInfo& di = device_info();
+  const Plan pl = make_plan(M, N, K, BITS, di.sms, max_ctas);
+  if (pl.stages < 2) return DXB_ERR_UNSUPPORTED;
+  const size_t need = kStatusBytes + counters_bytes(pl.tiles) +
+                      static_cast<size_t>(pl.tiles) * pl.max_slots * pl.NU * kTileN * sizeof(float);
+  if (workspace == nullptr || workspace_bytes < need) return DXB_ERR_WORKSPACE;
+
+  CUtensorMap tq, tx, ts, tz;
+  const int rows = pl.rows;
+  bool ok = make_map(&tq, qw, CU_TENSOR_MAP_DATA_TYPE_UINT8, N, rows, N, kTileN, kUnitRows,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+  ok = ok && make_map(&tx, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, K, M, ldx * 2, 64, pl.NU,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+  ok = ok && make_map(&ts, scales, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, N, K / group,
+                      static_cast<uint64_t>(N) * 2, kTileN, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (HAS_ZERO)
+    ok = ok && make_map(&tz, zeros, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, N, K / group,
+                        static_cast<uint64_t>(N) * 2, kTileN, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+  else
+    tz = ts;
+  if (!ok) return DXB_ERR_TENSORMAP;
+
+  WqParams p{};
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  uint8_t* wsb = static_cast<uint8_t*>(workspace);
+  p.status = reinterpret_cast<int*>(wsb);
+  p.counters = reinterpret_cast<int*>(wsb + kStatusBytes);
+  p.partials = reinterpret_cast<float*>(wsb + kStatusBytes + counters_bytes(pl.tiles));
+  p.M = M; p.N = N; p.K = K; p.group = group;
+  p.NU = pl.NU;
+  p.units_per_tile = pl.units_per_tile;
+  p.tiles = pl.tiles;
+  p.total_units = pl.total_units;
+  p.half_k = BITS == 4 ? K / 2 : 0;
+  p.stages = pl.stages;
+  p.x_stage_bytes = pl.x_stage_bytes;
+  p.max_slots = pl.max_slots;
+  p.nacc = pl.nacc;
+
+  auto kernel = wq_gemm_tc<BITS, HAS_ZERO>;
+  static thread_local int attr_dev[4] = {-1, -1, -1, -1};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int slot = (BITS == 8 ? 2 : 0) + (HAS_ZERO ? 1 : 0);
+  if (attr_dev[slot] != dev) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemBudget + 1024) != cudaSuccess)
+      return DXB_ERR_CUDA;
+    attr_dev[slot] = dev;
+  }
+  kernel<<<pl.ctas, kThreads, pl.smem_bytes, stream>>>(tq, tx, ts, tz, p);
+  return cudaGetLastError() == cudaSuccess ? DXB_OK : DXB_ERR_CUDA;
+}
+
+template <int BITS>
+static int launch_simt(const void* x, long long ldx, const void* qw, const void* scales,
+                       const void* zeros, const void* bias, void* out, long long ldo, int M, int N,
+                       int K, int group, cudaStream_t stream) {
+  dim3 block(128), grid((N + 127) / 128, (M + 7) / 8);
+  wq_gemm_simt<BITS><<<grid, block, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const uint8_t*>(qw),
+      static_cast<const __nv_bfloat16*>(scales), static_cast<const __nv_bfloat16*>(zeros),
+      static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(out), ldo, M, N, K, group);
+  return cudaGetLastError() == cudaSuccess ? DXB_OK : DXB_ERR_CUDA;
+}
+
+static int check_args(int bits, const void* x, long long ldx, const void* qw, const void* scales,
+                      void* out, long long ldo, int M, int N, int K, int group) {
+  if (bits != 4 && bits != 8) return DXB_ERR_BITS;
+  if (!x || !qw || !scales || !out) return DXB_ERR_NULL;
+  if (M < 0 || N <= 0 || K <= 0 || group <= 0) return DXB_ERR_SHAPE;
+  if (K % group) return DXB_ERR_SHAPE;
+  if (bits == 4 && (K % 2)) return DXB_ERR_SHAPE;
+  if (ldx < K || ldo < N) return DXB_ERR_SHAPE;
+  return DXB_OK;
+}
+
+}  // namespace dx
+
+// =================================================================== C ABI ==
+extern "C" {
+
+int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const void* scales,
+                const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
+                int group_size, void* workspace, size_t workspace_bytes, int max_ctas,
+                void* cuda_stream) {
+  using namespace dx;
+  int rc = check_args(bits, x, ldx, qweight, scales, out, ldo, M, N, K, group_size);
+  if (rc != DXB_OK) return rc;
+  if (M == 0) return DXB_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  const bool aligned = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) &&
+                       (reinterpret_cast<uintptr_t>(qweight) % 16 == 0) &&
+                       (reinterpret_cast<uintptr_t>(scales) % 16 == 0) &&
+                       (zeros == nullptr || reinterpret_cast<uintptr_t>(zeros) % 16 == 0);
+  // Token blocks of at most 256 rows per launch (128 keeps two accumulators in TMEM).
+  const int chunk = M <= 256 ? M : 128;
+  for (int m0 = 0; m0 < M; m0 += chunk) {
+    const int mc = (M - m0) < chunk ? (M - m0) : chunk;
+    const char* xc = static_cast<const char*>(x) + static_cast<long long>(m0) * ldx * 2;
+    char* oc = static_cast<char*>(out) + static_cast<long long>(m0) * ldo * 2;
+    if (aligned && tc_supported(mc, N, K, group_size, bits)) {
+      if (bits == 4)
+        rc = zeros ? launch_tc<4, true>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
+                                        group_size, workspace, workspace_bytes, max_ctas, stream)
+                   : launch_tc<4, false>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
+                                         group_size, workspace, workspace_bytes, max_ctas, stream);
+      else
+        rc = zeros ? launch_tc<8, true>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
+                                        group_size, workspace, workspace_bytes, max_ctas, stream)
+                   : launch_tc<8, false>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
+                                         group_size, workspace, workspace_bytes, max_ctas, stream);
+    } else {
+      rc = bits == 4 ? launch_simt<4>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
+                                      group_size, stream)
+                     : launch_simt<8>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
+                                      group_size, stream);
+    }
+    if (rc != DXB_OK) return rc;
+  }
+  return DXB_OK;
+}
+
+int dxb_w4a16(const void* x, int64_t ldx, const void* qweight, const void* scales,
+              const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
+              int group_size, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  return dxb_wq_gemm(4, x, ldx, qweight, scales, zeros, bias, out, ldo, M, N, K, group_size,
+                     workspace, workspace_bytes, 0, cuda_stream);
+}
+
+int dxb_w8a16(const void* x, int64_t ldx, const void* qweight, const void* scales,
+              const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
+              int group_size, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  return dxb_wq_gemm(8, x, ldx, qweight, scales, zeros, bias, out, ldo, M, N, K, group_size,
+                     workspace, workspace_bytes, 0, cuda_stream);
+}
+
+size_t dxb_workspace_bytes(int M, int N, int K, int bits) {
+  using namespace dx;
+  if (M <= 0 || N <= 0 || K <= 0 || (bits != 4 && bits != 8)) return kStatusBytes;
+  const int mc = M <= 256 ? M : 128;
+  const int rows = bits == 4 ? K / 2 : K;
+  if (rows < kUnitRows) return kStatusBytes;
+  DeviceInfo& di = device_info();
+  const Plan pl = make_plan(mc, N, K, bits, di.sms > 0 ? di.sms : 148, 0);
+  return kStatusBytes + counters_bytes(pl.tiles) +
+         static_cast<size_t>(pl.tiles) * pl.max_slots * pl.NU * kTileN * sizeof(float);
+}
+
+int dxb_dequantize(const void* qweight, const void* scales, const void* zeros, void* w_out, int N,
+                   int K, int group_size, int bits, void* cuda_stream) {
+  using namespace dx;
+  if (bits != 4 && bits != 8) return DXB_ERR_BITS;
+  if (!qweight || !scales || !w_out) return DXB_ERR_NULL;
+  if (N <= 0 || K <= 0 || group_size <= 0 || K % group_size || (bits == 4 && K % 2))
+    return DXB_ERR_SHAPE;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  const long long total = static_cast<long long>(K) * N;
+  const int block = 256;
+  const unsigned grid = static_cast<unsigned>((total + block - 1) / block);
+  if (bits == 4)
+    wq_dequant_kernel<4><<<grid, block, 0, stream>>>(
+        static_cast<const uint8_t*>(qweight), static_cast<const __nv_bfloat16*>(scales),
+        static_cast<const __nv_bfloat16*>(zeros), static_cast<__nv_bfloat16*>(w_out), N, K, group_size);
+  else
+    wq_dequant_kernel<8><<<grid, block, 0, stream>>>(
+        static_cast<const uint8_t*>(qweight), static_cast<const __nv_bfloat16*>(scales),
+        static_cast<const __nv_bfloat16*>(zeros), static_cast<__nv_bfloat16*>(w_out), N, K, group_size);
+  return cudaGetLastError() == cudaSuccess ? DXB_OK : DXB_ERR_CUDA;
+}
+
+int dxb_uses_tensor_cores(int M, int N, int K, int group_size, int bits) {
+  const int mc = M <= 256 ? M : 128;
+  return dx::tc_supported(mc, N, K, group_size, bits) ? 1 : 0;
+}
+
+int dxb_read_status(void* workspace, void* cuda_stream) {
+  if (!workspace) return DXB_ERR_NULL;
+  int code = 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (cudaMemcpyAsync(&code, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess)
+    return DXB_ERR_CUDA;
+  if (cudaStreamSynchronize(stream) != cudaSuccess) return DXB_ERR_CUDA;
+  return code;
+}
+
+const char* dxb_strerror(int code) {
+  switch (code) {
+    case DXB_OK: return "ok";
+    case DXB_ERR_BITS: return "bits must be 4 or 8";
+    case DXB_ERR_NULL: return "null pointer argument";
+    case DXB_ERR_SHAPE: return "inconsistent shape, stride or group size";
+    case DXB_ERR_UNSUPPORTED: return "shape not supported by this build";
+    case DXB_ERR_WORKSPACE: return "workspace missing or too small (see dxb_workspace_bytes)";
+    case DXB_ERR_TENSORMAP: return "could not encode a TMA tensor map";
+    case DXB_ERR_CUDA: return "CUDA launch or runtime error";
+    case DXB_ERR_KERNEL_TIMEOUT: return "a bounded wait inside the kernel ran out";
+    default: return "unknown error";
+  }
+}
+
+}  // extern "C"

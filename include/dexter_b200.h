@@ -1,0 +1,99 @@
+/*
+ * C ABI of the B200 (sm_100a) weight-only quantised GEMM backend.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer on the current
+ * CUDA device unless stated otherwise.  Calls enqueue work on `cuda_stream`
+ * (a cudaStream_t passed as void*) and do not synchronise, allocate or free
+ * device memory, so they can be recorded into a CUDA graph.  Every function
+ * returns DXB_OK (0) or a negative DXB_ERR_* code; nothing throws.
+ *
+ * The entry points are what a host binding for the reference's kernel slot
+ *     impl(x, qweight, scales, zeros, bias, group_size) -> Tensor
+ * needs (python/dexter/ops/reference/gemm.py:82-89 and
+ * python/dexter/ops/gfx1151/gemm/quantized.py:223-263 in the reference).
+ *
+ * Tensor layouts are the reference quantiser's (python/dexter/quant.py:34-133):
+ *   x        [M, K]    bf16, row stride `ldx` elements (>= K)
+ *   qweight  int4: [K/2, N] uint8, byte [i, n] = row i (low nibble) and row
+ *            i + K/2 (high nibble); int8: [K, N] uint8.  Row stride N.
+ *   scales   [K/group_size, N] bf16
+ *   zeros    [K/group_size, N] bf16 or NULL (symmetric: zero point 2^(bits-1));
+ *            4-bit zero points are stored with +128 added (quant.py:118-122)
+ *   bias     [N] bf16 or NULL
+ *   out      [M, N]    bf16, row stride `ldo` elements (>= N)
+ */
+#ifndef DEXTER_B200_H_
+#define DEXTER_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  DXB_OK = 0,
+  DXB_ERR_BITS = -1,           /* bits not 4 or 8  (ValueError in ops/__init__.py:110-111) */
+  DXB_ERR_NULL = -2,           /* a required pointer is NULL */
+  DXB_ERR_SHAPE = -3,          /* K vs group / packing / stride mismatch (quantized.py:225-226) */
+  DXB_ERR_UNSUPPORTED = -4,    /* shape outside what this build can run (quantized.py:220) */
+  DXB_ERR_WORKSPACE = -5,      /* workspace NULL or smaller than dxb_workspace_bytes() */
+  DXB_ERR_TENSORMAP = -6,      /* cuTensorMapEncodeTiled refused the tensor */
+  DXB_ERR_CUDA = -7,           /* launch failed; see cudaGetLastError */
+  DXB_ERR_KERNEL_TIMEOUT = -8  /* a bounded in-kernel wait ran out (read via dxb_read_status) */
+};
+
+/*
+ * out = x @ dequant(qweight, scales, zeros) (+ bias).
+ * Replaces the reference's _launch() + Triton kernel for `bits` = 4 or 8
+ * (python/dexter/ops/gfx1151/gemm/quantized.py:47-183, 223-249).
+ * `workspace` holds a status word, tile counters and split-K partial sums; it
+ * must be at least dxb_workspace_bytes() and zero-filled once before its first
+ * use (the kernel leaves it clean after every normal completion).  Two calls
+ * that may overlap on the GPU need different workspaces.
+ * `max_ctas` <= 0 lets the library use every SM; a positive value caps the grid.
+ */
+int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const void* scales,
+                const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
+                int group_size, void* workspace, size_t workspace_bytes, int max_ctas,
+                void* cuda_stream);
+
+/* The registered kernels gemm/w4a16 and gemm/w8a16
+ * (python/dexter/ops/gfx1151/gemm/quantized.py:252-263). */
+int dxb_w4a16(const void* x, int64_t ldx, const void* qweight, const void* scales,
+              const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
+              int group_size, void* workspace, size_t workspace_bytes, void* cuda_stream);
+int dxb_w8a16(const void* x, int64_t ldx, const void* qweight, const void* scales,
+              const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
+              int group_size, void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/* Bytes of workspace dxb_wq_gemm needs for this problem on the current device. */
+size_t dxb_workspace_bytes(int M, int N, int K, int bits);
+
+/*
+ * Dense [K, N] bf16 weight, computed with the same bit-pattern arithmetic as the
+ * GEMM kernel.  Replaces the reference's dequantize()
+ * (python/dexter/ops/reference/gemm.py:51-73); used to check dequantisation
+ * bit for bit.
+ */
+int dxb_dequantize(const void* qweight, const void* scales, const void* zeros, void* w_out, int N,
+                   int K, int group_size, int bits, void* cuda_stream);
+
+/* 1 when dxb_wq_gemm runs this shape on the tcgen05 kernel, 0 when it takes the
+ * plain CUDA-core kernel (the counterpart of the reference's `accepts` shape
+ * predicate, python/dexter/registry.py:58-60). */
+int dxb_uses_tensor_cores(int M, int N, int K, int group_size, int bits);
+
+/* Synchronises `cuda_stream` and returns the status word of `workspace`:
+ * DXB_OK, or DXB_ERR_KERNEL_TIMEOUT if a kernel gave up on a wait. */
+int dxb_read_status(void* workspace, void* cuda_stream);
+
+/* Static, NUL-terminated description of a DXB_* code. */
+const char* dxb_strerror(int code);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* DEXTER_B200_H_ */
