@@ -30,6 +30,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 #include <cuda.h>
@@ -40,22 +41,26 @@
 #include "sm100_ptx.cuh"
 
 namespace dx {
+#define DX_TRACE(role, i) do { if (p.trace && (i) < 32) p.trace[(static_cast<long long>(blockIdx.x) * 8 + (role)) * 32 + (i)] = clock64() - t_start; } while (0)
 
 // ------------------------------------------------------------------ constants
 constexpr int kTileN = 128;      // weight columns per tile (UMMA M)
 constexpr int kUnitRows = 64;    // packed rows per pipeline unit
 constexpr int kQBytes = kTileN * kUnitRows;  // 8192
-constexpr int kWStage = kQBytes + 1024;      // + 2 scale rows + 2 zero rows of 256 B
-constexpr int kMaxStages = 8;
+constexpr int kWStage = kQBytes;
+constexpr int kMaxStages = 8;    // activation ring
+constexpr int kMaxWStages = 16;  // packed-weight ring; always a multiple of kAStages
 constexpr int kAStages = 4;      // dequantised-tile ring in TMEM
 constexpr int kACol0 = 256;      // TMEM column where that ring starts
-constexpr int kThreads = 448;    // 14 warps
-constexpr int kDequantThreads = 256;
+constexpr int kThreads = 768;    // 24 warps
+constexpr int kDequantThreads = 128;  // one team
 constexpr int kEpilogueThreads = 128;
 constexpr int kSmemBudget = 227 * 1024 - 4096;
 constexpr int kMaxTiles = 16384;  // tile counters reserved in every workspace
 
 struct WqParams {
+  const __nv_bfloat16* scales;
+  const __nv_bfloat16* zeros;
   const __nv_bfloat16* bias;
   __nv_bfloat16* out;
   long long ldo;
@@ -68,17 +73,14 @@ struct WqParams {
   int tiles;           // ceil(N / 128)
   int total_units;
   int half_k;          // int4: K/2 (first activation column of the high-nibble plane)
-  int stages;
+  int stages;          // activation (X) ring depth
+  int w_stages;        // packed-weight ring depth, a multiple of 4 so that every
+                       // stage is only ever used by one dequant team, in order
   int x_stage_bytes;   // planes * NU * 128
   int max_slots;       // partial slots reserved per tile
   int nacc;            // accumulator buffers in TMEM (2 when NU <= 128)
-};
-
-struct alignas(8) Barriers {
-  uint64_t full_w[kMaxStages], empty_w[kMaxStages];
-  uint64_t full_x[kMaxStages], empty_x[kMaxStages];
-  uint64_t a_full[kAStages], a_empty[kAStages];
-  uint64_t acc_full[2], acc_empty[2];
+  int dbg;
+  long long* trace;
 };
 
 // -------------------------------------------------------------- dequant math
@@ -146,51 +148,55 @@ __host__ __device__ inline int owner_of(long long u, long long total, long long 
 }
 
 // ----------------------------------------------------------------- the kernel
+// Barrier slots in shared memory.
+constexpr int kBarFullW = 0, kBarEmptyW = 16, kBarFullX = 32, kBarEmptyX = 40, kBarAFull = 48,
+              kBarAEmpty = 52, kBarAccFull = 56, kBarAccEmpty = 58, kNumBars = 60;
+
+__device__ __forceinline__ uint32_t bar_count(int i) {
+  if (i < kBarEmptyW) return 1;                 // full_w: producer's expect_tx
+  if (i < kBarFullX) return kDequantThreads;    // empty_w: every dequant thread
+  if (i < kBarAFull) return 1;                  // full_x (expect_tx), empty_x (commit)
+  if (i < kBarAEmpty) return kDequantThreads;   // a_full
+  if (i < kBarAccEmpty) return 1;               // a_empty, acc_full (commit)
+  return kEpilogueThreads;                      // acc_empty
+}
+
 template <int BITS, bool HAS_ZERO>
 __global__ void __launch_bounds__(kThreads, 1)
 wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_x,
-           const __grid_constant__ CUtensorMap tm_s, const __grid_constant__ CUtensorMap tm_z,
            const WqParams p) {
   constexpr int PLANES = BITS == 4 ? 2 : 1;
   constexpr int A_STAGE_COLS = PLANES * 32;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ Barriers bars;
+  __shared__ __align__(8) uint64_t bars[kNumBars];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   __shared__ int last_flag;
+  __shared__ long long t_start;
 
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t w_ring = smem0;
-  const uint32_t x_ring = smem0 + p.stages * kWStage;
+  const uint32_t x_ring = smem0 + p.w_stages * kWStage;
+  const uint32_t bar0 = smem_u32(bars);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int S = p.stages;
+  const int SW = p.w_stages;
 
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-    last_flag = 0;
-    for (int s = 0; s < kMaxStages; ++s) {
-      mbar_init(smem_u32(&bars.full_w[s]), 1);
-      mbar_init(smem_u32(&bars.empty_w[s]), kDequantThreads);
-      mbar_init(smem_u32(&bars.full_x[s]), 1);
-      mbar_init(smem_u32(&bars.empty_x[s]), 1);
-    }
-    for (int t = 0; t < kAStages; ++t) {
-      mbar_init(smem_u32(&bars.a_full[t]), kDequantThreads);
-      mbar_init(smem_u32(&bars.a_empty[t]), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&bars.acc_full[b]), 1);
-      mbar_init(smem_u32(&bars.acc_empty[b]), kEpilogueThreads);
+  if (warp == 3) {
+    for (int i = lane; i < kNumBars; i += 32) mbar_init(bar0 + 8 * i, bar_count(i));
+    if (lane == 0) {
+      t_start = clock64();
+      abort_flag = 0;
+      last_flag = 0;
     }
     mbar_init_fence();
+  } else if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tm_q);
+  } else if (warp == 2 && lane == 0) {
     tma_prefetch_desc(&tm_x);
-    tma_prefetch_desc(&tm_s);
-    if (HAS_ZERO) tma_prefetch_desc(&tm_z);
-  }
-  if (warp == 1) {
+  } else if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_base_s), 512);
     tmem_relinquish();
   }
@@ -200,173 +206,222 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const uint32_t tmem0 = tmem_base_s;
 
   // This CTA's contiguous range of (tile, unit) work.
-  const long long TU = p.total_units;
-  const long long G = gridDim.x;
-  const long long u_begin = range_begin(blockIdx.x, TU, G);
-  const long long u_end = range_begin(blockIdx.x + 1, TU, G);
+  const int TU = p.total_units;
+  const int G = static_cast<int>(gridDim.x);
+  const int u_begin = static_cast<int>(range_begin(blockIdx.x, TU, G));
+  const int u_end = static_cast<int>(range_begin(blockIdx.x + 1, TU, G));
   const int U = p.units_per_tile;
+  const int tile_begin = u_begin / U;
+  const int ku_begin = u_begin - tile_begin * U;
   volatile int* abortp = &abort_flag;
 
   if (warp == 0) {
-    // ===================================================== TMA producer ====
-    if (lane == 0) {
-      const uint32_t w_bytes = kQBytes + PLANES * 256 * (HAS_ZERO ? 2 : 1);
-      const uint32_t x_bytes = p.x_stage_bytes;
-      long long it = 0;
+    // ============================================ TMA producer: packed weights
+    // The whole warp runs the loop (so addresses and coordinates stay in uniform
+    // registers, which the TMA instruction wants); one elected lane issues.
+    {
+      int tile = tile_begin, ku = ku_begin, s = 0;
+      uint32_t ph = 0;
+      int issued = 0;
       bool ok = true;
-      for (long long u = u_begin; u < u_end && ok; ++u, ++it) {
-        const int tile = static_cast<int>(u / U);
-        const int ku = static_cast<int>(u % U);
-        const int s = static_cast<int>(it % S);
-        const uint32_t ph = static_cast<uint32_t>(it / S) & 1u;
-        ok = mbar_wait(smem_u32(&bars.empty_w[s]), ph ^ 1u, abortp) &&
-             mbar_wait(smem_u32(&bars.empty_x[s]), ph ^ 1u, abortp);
+      for (int u = u_begin; u < u_end; ++u) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarEmptyW + s), ph ^ 1u, abortp));
         if (!ok) break;
-        const uint32_t wdst = w_ring + s * kWStage;
-        const uint32_t xdst = x_ring + s * p.x_stage_bytes;
-        const uint32_t fw = smem_u32(&bars.full_w[s]);
-        const uint32_t fx = smem_u32(&bars.full_x[s]);
-        const int n0 = tile * kTileN;
-        const int r0 = ku * kUnitRows;
-        mbar_expect_tx(fw, w_bytes);
-        tma_load_2d(wdst, &tm_q, fw, n0, r0);
-#pragma unroll
-        for (int pl = 0; pl < PLANES; ++pl) {
-          const int k0 = r0 + pl * p.half_k;
-          const int g = k0 / p.group;
-          tma_load_2d(wdst + kQBytes + pl * 256, &tm_s, fw, n0, g);
-          if (HAS_ZERO) tma_load_2d(wdst + kQBytes + 512 + pl * 256, &tm_z, fw, n0, g);
+        if (elect_one()) {
+          const uint32_t fw = bar0 + 8 * (kBarFullW + s);
+          mbar_expect_tx(fw, kQBytes);
+          tma_load_2d(w_ring + s * kWStage, &tm_q, fw, tile * kTileN, ku * kUnitRows);
         }
-        mbar_expect_tx(fx, x_bytes);
-#pragma unroll
-        for (int pl = 0; pl < PLANES; ++pl)
-          tma_load_2d(xdst + pl * p.NU * 128, &tm_x, fx, r0 + pl * p.half_k, 0);
+        __syncwarp();
+        ++issued;
+        if (++s == SW) { s = 0; ph ^= 1u; }
+        if (++ku == U) { ku = 0; ++tile; }
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         // Leaving early: let the copies already issued land before the CTA exits.
-        for (long long j = (it > S ? it - S : 0); j < it; ++j) {
-          const int s = static_cast<int>(j % S);
-          const uint32_t ph = static_cast<uint32_t>(j / S) & 1u;
+        for (int j = (issued > SW ? issued - SW : 0); j < issued; ++j)
           for (int spin = 0; spin < 200000; ++spin)
-            if (mbar_try_wait(smem_u32(&bars.full_w[s]), ph) &&
-                mbar_try_wait(smem_u32(&bars.full_x[s]), ph))
+            if (mbar_try_wait(bar0 + 8 * (kBarFullW + j % SW), static_cast<uint32_t>(j / SW) & 1u))
               break;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 2) {
+    // ============================================== TMA producer: activations
+    {
+      int ku = ku_begin, s = 0;
+      uint32_t ph = 0;
+      int issued = 0;
+      bool ok = true;
+      const uint32_t x_bytes = p.x_stage_bytes;
+      for (int u = u_begin; u < u_end; ++u) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarEmptyX + s), ph ^ 1u, abortp));
+        if (!ok) break;
+        if (elect_one()) {
+          const uint32_t fx = bar0 + 8 * (kBarFullX + s);
+          mbar_expect_tx(fx, x_bytes);
+          if (BITS == 4)
+            tma_load_3d(x_ring + s * p.x_stage_bytes, &tm_x, fx, ku * kUnitRows, 0, 0);
+          else
+            tma_load_2d(x_ring + s * p.x_stage_bytes, &tm_x, fx, ku * kUnitRows, 0);
         }
+        __syncwarp();
+        ++issued;
+        if (++s == S) { s = 0; ph ^= 1u; }
+        if (++ku == U) ku = 0;
+      }
+      if (!ok && lane == 0) {
+        for (int j = (issued > S ? issued - S : 0); j < issued; ++j)
+          for (int spin = 0; spin < 200000; ++spin)
+            if (mbar_try_wait(bar0 + 8 * (kBarFullX + j % S), static_cast<uint32_t>(j / S) & 1u))
+              break;
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ======================================================= MMA issuer ====
-    if (lane == 0) {
+    // Warp-uniform loop as well: descriptors, TMEM addresses and barrier addresses
+    // live in uniform registers; one elected lane issues the MMAs and commits.
+    {
       const uint32_t idesc = idesc_bf16_f32(kTileN, p.NU);
       const uint64_t xdesc0 = smem_desc_kmajor_sw128(x_ring);
       const uint32_t x_stage16 = static_cast<uint32_t>(p.x_stage_bytes) >> 4;
       const uint32_t plane16 = static_cast<uint32_t>(p.NU * 128) >> 4;
-      long long it = 0;
-      int seg = 0;
+      int s = 0, t = 0, b = 0;
+      uint32_t ph = 0, aph = 0, accph = 0;
+      uint64_t xd = xdesc0;
+      uint32_t a_tmem = tmem0 + kACol0;
       bool ok = true;
-      long long u = u_begin;
+      int u = u_begin, ku0 = ku_begin, done = 0;
       while (u < u_end && ok) {
-        const int ku0 = static_cast<int>(u % U);
-        const long long left = u_end - u;
-        const int nun = static_cast<int>(left < (U - ku0) ? left : (U - ku0));
-        const int b = seg % p.nacc;
-        const uint32_t accph = static_cast<uint32_t>(seg / p.nacc) & 1u;
-        ok = mbar_wait(smem_u32(&bars.acc_empty[b]), accph ^ 1u, abortp);
+        const int left = u_end - u;
+        const int nun = left < (U - ku0) ? left : (U - ku0);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarAccEmpty + b), accph ^ 1u, abortp));
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem0 + b * p.NU;
-        for (int i = 0; i < nun; ++i, ++it) {
-          const int s = static_cast<int>(it % S);
-          const uint32_t ph = static_cast<uint32_t>(it / S) & 1u;
-          const int t = static_cast<int>(it % kAStages);
-          const uint32_t aph = static_cast<uint32_t>(it / kAStages) & 1u;
-          ok = mbar_wait(smem_u32(&bars.full_x[s]), ph, abortp) &&
-               mbar_wait(smem_u32(&bars.a_full[t]), aph, abortp);
+        for (int i = 0; i < nun; ++i) {
+          ok = mbar_wait(bar0 + 8 * (kBarFullX + s), ph, abortp);
+          ok = mbar_wait(bar0 + 8 * (kBarAFull + t), aph, abortp) && ok;
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
-          const uint64_t xd = xdesc0 + static_cast<uint64_t>(s * x_stage16);
-          const uint32_t a_tmem = tmem0 + kACol0 + t * A_STAGE_COLS;
-#pragma unroll
-          for (int pl = 0; pl < PLANES; ++pl) {
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              mma_ts(d_tmem, a_tmem + pl * 32 + kk * 8, xd + pl * plane16 + kk * 2, idesc,
-                     (i | pl | kk) != 0);
+          if (elect_one()) {
+            if (i == 0) {
+              mma_ts(d_tmem, a_tmem, xd, idesc, 0u);
+            } else {
+              mma_ts(d_tmem, a_tmem, xd, idesc, 1u);
             }
+#pragma unroll
+            for (int kk = 1; kk < 4; ++kk) mma_ts(d_tmem, a_tmem + kk * 8, xd + kk * 2, idesc, 1u);
+            if (PLANES == 2) {
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                mma_ts(d_tmem, a_tmem + 32 + kk * 8, xd + plane16 + kk * 2, idesc, 1u);
+            }
+            tc_commit(bar0 + 8 * (kBarAEmpty + t));
+            tc_commit(bar0 + 8 * (kBarEmptyX + s));
           }
-          tc_commit(smem_u32(&bars.a_empty[t]));
-          tc_commit(smem_u32(&bars.empty_x[s]));
+          __syncwarp();
+          if (lane == 0) DX_TRACE(3, done);
+          ++done;
+          xd += x_stage16;
+          if (++s == S) { s = 0; ph ^= 1u; xd = xdesc0; }
+          a_tmem += A_STAGE_COLS;
+          if (++t == kAStages) { t = 0; aph ^= 1u; a_tmem = tmem0 + kACol0; }
         }
         if (!ok) break;
-        tc_commit(smem_u32(&bars.acc_full[b]));
+        if (elect_one()) tc_commit(bar0 + 8 * (kBarAccFull + b));
+        __syncwarp();
         u += nun;
-        ++seg;
+        ku0 = 0;
+        if (++b == p.nacc) { b = 0; accph ^= 1u; }
       }
     }
     __syncwarp();
-  } else if (warp < 6) {
+  } else if (warp >= 4 && warp < 8) {
     // ========================================================= epilogue ====
-    const int q = warp & 3;                       // this warp's TMEM lane quadrant
-    const int etid = (warp - 2) * 32 + lane;      // 0..127 within the epilogue group
-    // TMEM lane -> weight column inside the tile (see the dequant mapping below).
-    const int n_local = 32 * q + 4 * (lane & 7) + (lane >> 3);
-    int seg = 0;
+    // Accumulator lane 32q + 8b + g holds weight column 32q + 4g + b (see the
+    // dequant mapping), so the 16x128b load shape hands thread (g, c) the four
+    // consecutive columns 4g..4g+3 of token 4*rep + c: one 8-byte store each.
+    const int q = warp & 3;
+    const int etid = (warp - 4) * 32 + lane;
+    const int c = lane & 3;
+    const int g = lane >> 2;
+    const int n_local = 32 * q + 4 * g;
+    const bool has_bias = p.bias != nullptr;
+    int b = 0;
+    uint32_t accph = 0;
     bool ok = true;
-    long long u = u_begin;
+    int u = u_begin, ku0 = ku_begin, tile = tile_begin;
     while (u < u_end && ok) {
-      const int tile = static_cast<int>(u / U);
-      const int ku0 = static_cast<int>(u % U);
-      const long long left = u_end - u;
-      const int nun = static_cast<int>(left < (U - ku0) ? left : (U - ku0));
+      const int left = u_end - u;
+      const int nun = left < (U - ku0) ? left : (U - ku0);
       const bool whole = (nun == U);
-      const int b = seg % p.nacc;
-      const uint32_t accph = static_cast<uint32_t>(seg / p.nacc) & 1u;
-      ok = mbar_wait(smem_u32(&bars.acc_full[b]), accph, abortp);
+      ok = mbar_wait(bar0 + 8 * (kBarAccFull + b), accph, abortp);
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_addr(tmem0 + b * p.NU, 32 * q, 0);
       const int n = tile * kTileN + n_local;
+      const bool n_ok = n < p.N;
       if (whole) {
-        const float bias = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
-        const bool has_bias = p.bias != nullptr;
+        float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (has_bias && n_ok) {
+          const uint2 bb = *reinterpret_cast<const uint2*>(p.bias + n);
+          bias4[0] = bf16lo_f32(bb.x); bias4[1] = bf16hi_f32(bb.x);
+          bias4[2] = bf16lo_f32(bb.y); bias4[3] = bf16hi_f32(bb.y);
+        }
         for (int c0 = 0; c0 < p.NU; c0 += 16) {
-          uint32_t v[16];
-          tmem_ld_32x32b_x16(d_tmem + c0, v);
+          uint32_t ra[8], rb[8];
+          tmem_ld_16x128b_x4(d_tmem + c0, ra);
+          tmem_ld_16x128b_x4(d_tmem + (16u << 16) + c0, rb);
           tc_wait_ld();
-          if (n < p.N) {
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              const int m = c0 + c;
-              if (m < p.M) {
-                __nv_bfloat16 o = __float2bfloat16_rn(__uint_as_float(v[c]));
-                if (has_bias) o = __float2bfloat16_rn(__bfloat162float(o) + bias);
-                p.out[static_cast<long long>(m) * p.ldo + n] = o;
+          for (int rep = 0; rep < 4; ++rep) {
+            const int m = c0 + 4 * rep + c;
+            if (n_ok && m < p.M) {
+              const float f[4] = {__uint_as_float(ra[2 * rep]), __uint_as_float(ra[2 * rep + 1]),
+                                  __uint_as_float(rb[2 * rep]), __uint_as_float(rb[2 * rep + 1])};
+              uint2 pk;
+              if (has_bias) {
+                // Reference order: round the matmul to bf16, then add the bias in bf16.
+                const uint32_t r01 = cvt_bf16x2(f[1], f[0]), r23 = cvt_bf16x2(f[3], f[2]);
+                pk.x = cvt_bf16x2(bf16hi_f32(r01) + bias4[1], bf16lo_f32(r01) + bias4[0]);
+                pk.y = cvt_bf16x2(bf16hi_f32(r23) + bias4[3], bf16lo_f32(r23) + bias4[2]);
+              } else {
+                pk.x = cvt_bf16x2(f[1], f[0]);
+                pk.y = cvt_bf16x2(f[3], f[2]);
               }
+              *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.ldo + n) = pk;
             }
           }
         }
         tc_fence_before();
-        mbar_arrive(smem_u32(&bars.acc_empty[b]));
+        mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
       } else {
         // Partial tile: park the fp32 sums, then whoever completes the tile reduces.
         const int c_first = owner_of(static_cast<long long>(tile) * U, TU, G);
         const int c_last = owner_of(static_cast<long long>(tile) * U + U - 1, TU, G);
         const int slot = static_cast<int>(blockIdx.x) - c_first;
-        float* ws = p.partials +
-                    (static_cast<long long>(tile) * p.max_slots + slot) * p.NU * kTileN;
+        const long long slot_elems = static_cast<long long>(p.NU) * kTileN;
+        float* tile_ws = p.partials + static_cast<long long>(tile) * p.max_slots * slot_elems;
+        float* ws = tile_ws + slot * slot_elems;
         for (int c0 = 0; c0 < p.NU; c0 += 16) {
-          uint32_t v[16];
-          tmem_ld_32x32b_x16(d_tmem + c0, v);
+          uint32_t ra[8], rb[8];
+          tmem_ld_16x128b_x4(d_tmem + c0, ra);
+          tmem_ld_16x128b_x4(d_tmem + (16u << 16) + c0, rb);
           tc_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const int m = c0 + c;
-            if (m < p.M) ws[m * kTileN + n_local] = __uint_as_float(v[c]);
+          for (int rep = 0; rep < 4; ++rep) {
+            const int m = c0 + 4 * rep + c;
+            if (m < p.M)
+              __stcg(reinterpret_cast<float4*>(ws + m * kTileN + n_local),
+                     make_float4(__uint_as_float(ra[2 * rep]), __uint_as_float(ra[2 * rep + 1]),
+                                 __uint_as_float(rb[2 * rep]), __uint_as_float(rb[2 * rep + 1])));
           }
         }
         tc_fence_before();
-        mbar_arrive(smem_u32(&bars.acc_empty[b]));
+        mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
         __threadfence();
         named_bar_sync(1, kEpilogueThreads);
         if (etid == 0) {
@@ -378,72 +433,124 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
         named_bar_sync(1, kEpilogueThreads);
         if (last_flag) {
+          // 128 threads = 32 groups of 4 columns x 4 row phases; slots are summed in
+          // slot order, so the result does not depend on which CTA arrives last.
           const int nslots = c_last - c_first + 1;
-          const int nn = tile * kTileN + etid;
-          const float* base =
-              p.partials + static_cast<long long>(tile) * p.max_slots * p.NU * kTileN + etid;
+          const int col4 = (etid & 31) * 4;
+          const int nn = tile * kTileN + col4;
           if (nn < p.N) {
-            const bool has_bias = p.bias != nullptr;
-            const float bias = has_bias ? __bfloat162float(p.bias[nn]) : 0.0f;
-            for (int m = 0; m < p.M; ++m) {
-              float acc = 0.0f;
-              for (int sl = 0; sl < nslots; ++sl)
-                acc += __ldcg(base + (static_cast<long long>(sl) * p.NU + m) * kTileN);
-              __nv_bfloat16 o = __float2bfloat16_rn(acc);
-              if (has_bias) o = __float2bfloat16_rn(__bfloat162float(o) + bias);
-              p.out[static_cast<long long>(m) * p.ldo + nn] = o;
+            float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (has_bias) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) bias4[j] = __bfloat162float(p.bias[nn + j]);
+            }
+            for (int m0 = etid >> 5; m0 < p.M; m0 += 16) {
+              float4 acc[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int sl = 0; sl < nslots; ++sl) {
+                float4 v[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int m = m0 + 4 * j;
+                  v[j] = m < p.M ? __ldcg(reinterpret_cast<const float4*>(
+                                       tile_ws + sl * slot_elems + m * kTileN + col4))
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  acc[j].x += v[j].x; acc[j].y += v[j].y; acc[j].z += v[j].z; acc[j].w += v[j].w;
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int m = m0 + 4 * j;
+                if (m < p.M) {
+                  uint2 pk;
+                  if (has_bias) {
+                    const uint32_t r01 = cvt_bf16x2(acc[j].y, acc[j].x);
+                    const uint32_t r23 = cvt_bf16x2(acc[j].w, acc[j].z);
+                    pk.x = cvt_bf16x2(bf16hi_f32(r01) + bias4[1], bf16lo_f32(r01) + bias4[0]);
+                    pk.y = cvt_bf16x2(bf16hi_f32(r23) + bias4[3], bf16lo_f32(r23) + bias4[2]);
+                  } else {
+                    pk.x = cvt_bf16x2(acc[j].y, acc[j].x);
+                    pk.y = cvt_bf16x2(acc[j].w, acc[j].z);
+                  }
+                  *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.ldo + nn) = pk;
+                }
+              }
             }
           }
         }
         named_bar_sync(1, kEpilogueThreads);  // last_flag is reused by the next segment
       }
       u += nun;
-      ++seg;
+      ku0 = 0;
+      ++tile;
+      if (++b == p.nacc) { b = 0; accph ^= 1u; }
     }
-  } else {
+  } else if (warp >= 8) {
     // ========================================================== dequant ====
+    // Four teams of four warps; team j converts units j, j+4, j+8, ... of this CTA
+    // into TMEM ring stage j, so four units are in flight and the per-unit chain
+    // (barrier wake-up, shared-memory loads, TMEM store drain) of one team is
+    // hidden behind the other three.
     // Thread (c = lane % 4, g = lane / 4) of quadrant q reads, for each slab of 8
     // packed rows, the 32-bit words at rows 2c and 2c+1, byte columns
     // 32q + 4g .. +3.  Byte b of the word is weight column 32q + 4g + b and goes to
     // TMEM lane 32q + 8b + g; rows (2c, 2c+1) form one bf16 pair = TMEM column c of
     // that slab: exactly the register layout of tcgen05.st.16x128b.
+    const int team = (warp - 8) >> 2;
     const int q = warp & 3;
-    const int rh = (warp - 6) >> 2;  // which 32 of the unit's 64 rows
     const int c = lane & 3;
     const int g = lane >> 2;
     const uint32_t chunk = 2 * q + (g >> 2);
-    const uint32_t row0 = 32 * rh + 2 * c;
-    const uint32_t off0 = row0 * 128 + ((chunk ^ (2 * c)) << 4) + 4 * (g & 3);
-    const uint32_t off1 = (row0 + 1) * 128 + ((chunk ^ (2 * c + 1)) << 4) + 4 * (g & 3);
-    const uint32_t sc_off = kQBytes + (32 * q + 4 * g) * 2;
+    const uint32_t off0 = (2 * c) * 128 + ((chunk ^ (2 * c)) << 4) + 4 * (g & 3);
+    const uint32_t off1 = (2 * c + 1) * 128 + ((chunk ^ (2 * c + 1)) << 4) + 4 * (g & 3);
     const uint32_t lane_base = 32 * q;
-    long long it = 0;
+    const int n_local = 32 * q + 4 * g;
+    const int group_units = p.group / kUnitRows;
+    const int half_units = p.half_k / kUnitRows;
+    const uint2* sc_ptr = reinterpret_cast<const uint2*>(p.scales);
+    const uint2* zr_ptr = reinterpret_cast<const uint2*>(p.zeros);
+    const uint32_t a_tmem = tmem0 + kACol0 + team * A_STAGE_COLS;
+    const uint32_t a_full_bar = bar0 + 8 * (kBarAFull + team);
+    const uint32_t a_empty_bar = bar0 + 8 * (kBarAEmpty + team);
+
+    // cursor of this team's current unit
+    int u = u_begin + team;
+    int tile = tile_begin, ku = ku_begin + team;
+    while (ku >= U) { ku -= U; ++tile; }
+    int s = team;  // SW is a multiple of the team count: stages j, j+4, ... belong to team j
+    uint32_t ph = 0;
+    uint32_t aph = 0;
     bool ok = true;
-    for (long long u = u_begin; u < u_end && ok; ++u, ++it) {
-      const int s = static_cast<int>(it % S);
-      const uint32_t ph = static_cast<uint32_t>(it / S) & 1u;
-      const int t = static_cast<int>(it % kAStages);
-      const uint32_t aph = static_cast<uint32_t>(it / kAStages) & 1u;
-      ok = mbar_wait(smem_u32(&bars.full_w[s]), ph, abortp);
+    for (; u < u_end; u += kAStages) {
+      // scales / zero points for this unit, straight from global (L2-resident)
+      uint2 sc[PLANES], zr[PLANES];
+      {
+        const int n = tile * kTileN + n_local;
+#pragma unroll
+        for (int pl = 0; pl < PLANES; ++pl) {
+          const int grp = (ku + pl * half_units) / group_units;
+          const long long idx = (static_cast<long long>(grp) * p.N + n) >> 2;
+          sc[pl] = n < p.N ? __ldg(sc_ptr + idx) : make_uint2(0u, 0u);
+          if (HAS_ZERO) zr[pl] = n < p.N ? __ldg(zr_ptr + idx) : make_uint2(0u, 0u);
+        }
+      }
+      ok = mbar_wait(bar0 + 8 * (kBarFullW + s), ph, abortp);
       if (!ok) break;
       const uint32_t wsrc = w_ring + s * kWStage;
-      uint32_t w0[4], w1[4];
+      uint32_t w0[8], w1[8];
 #pragma unroll
-      for (int sl = 0; sl < 4; ++sl) {
+      for (int sl = 0; sl < 8; ++sl) {
         w0[sl] = lds32(wsrc + off0 + sl * 1024);
         w1[sl] = lds32(wsrc + off1 + sl * 1024);
       }
-      uint2 sc[PLANES], zr[PLANES];
-#pragma unroll
-      for (int pl = 0; pl < PLANES; ++pl) {
-        sc[pl] = lds64(wsrc + sc_off + pl * 256);
-        if (HAS_ZERO) zr[pl] = lds64(wsrc + sc_off + 512 + pl * 256);
-      }
-      mbar_arrive(smem_u32(&bars.empty_w[s]));  // packed stage is in registers now
-      ok = mbar_wait(smem_u32(&bars.a_empty[t]), aph ^ 1u, abortp);
+      mbar_arrive(bar0 + 8 * (kBarEmptyW + s));  // packed stage is in registers now
+      ok = mbar_wait(a_empty_bar, aph ^ 1u, abortp);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t a_tmem = tmem0 + kACol0 + t * A_STAGE_COLS + 16 * rh;
       if (BITS == 4) {
 #pragma unroll
         for (int pl = 0; pl < 2; ++pl) {
@@ -456,18 +563,21 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           } else {
             z2[0] = z2[1] = z2[2] = z2[3] = 0x43084308u;  // 128 + 8
           }
-          uint32_t ra[8], rb[8];
 #pragma unroll
-          for (int sl = 0; sl < 4; ++sl) {
-            const uint32_t P = prmt(w0[sl], w1[sl], 0x5410u) >> (4 * pl);
-            const uint32_t Q = prmt(w0[sl], w1[sl], 0x7632u) >> (4 * pl);
-            ra[2 * sl + 0] = deq4(P, z2[0], s2[0]);
-            ra[2 * sl + 1] = deq4(P >> 8, z2[1], s2[1]);
-            rb[2 * sl + 0] = deq4(Q, z2[2], s2[2]);
-            rb[2 * sl + 1] = deq4(Q >> 8, z2[3], s2[3]);
+          for (int rh = 0; rh < 2; ++rh) {
+            uint32_t ra[8], rb[8];
+#pragma unroll
+            for (int sl = 0; sl < 4; ++sl) {
+              const uint32_t P = prmt(w0[4 * rh + sl], w1[4 * rh + sl], 0x5410u) >> (4 * pl);
+              const uint32_t Q = prmt(w0[4 * rh + sl], w1[4 * rh + sl], 0x7632u) >> (4 * pl);
+              ra[2 * sl + 0] = deq4(P, z2[0], s2[0]);
+              ra[2 * sl + 1] = deq4(P >> 8, z2[1], s2[1]);
+              rb[2 * sl + 0] = deq4(Q, z2[2], s2[2]);
+              rb[2 * sl + 1] = deq4(Q >> 8, z2[3], s2[3]);
+            }
+            tmem_st_16x128b_x4(tmem_addr(a_tmem + pl * 32 + 16 * rh, lane_base, 0), ra);
+            tmem_st_16x128b_x4(tmem_addr(a_tmem + pl * 32 + 16 * rh, lane_base + 16, 0), rb);
           }
-          tmem_st_16x128b_x4(tmem_addr(a_tmem + pl * 32, lane_base, 0), ra);
-          tmem_st_16x128b_x4(tmem_addr(a_tmem + pl * 32, lane_base + 16, 0), rb);
         }
       } else {
         const float sf[4] = {bf16lo_f32(sc[0].x), bf16hi_f32(sc[0].x), bf16lo_f32(sc[0].y),
@@ -479,25 +589,36 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         } else {
           cz[0] = cz[1] = cz[2] = cz[3] = 8388608.0f + 128.0f;
         }
-        uint32_t ra[8], rb[8];
 #pragma unroll
-        for (int sl = 0; sl < 4; ++sl) {
-          ra[2 * sl + 0] = cvt_bf16x2(deq8(w1[sl], 0, cz[0], sf[0]), deq8(w0[sl], 0, cz[0], sf[0]));
-          ra[2 * sl + 1] = cvt_bf16x2(deq8(w1[sl], 1, cz[1], sf[1]), deq8(w0[sl], 1, cz[1], sf[1]));
-          rb[2 * sl + 0] = cvt_bf16x2(deq8(w1[sl], 2, cz[2], sf[2]), deq8(w0[sl], 2, cz[2], sf[2]));
-          rb[2 * sl + 1] = cvt_bf16x2(deq8(w1[sl], 3, cz[3], sf[3]), deq8(w0[sl], 3, cz[3], sf[3]));
+        for (int rh = 0; rh < 2; ++rh) {
+          uint32_t ra[8], rb[8];
+#pragma unroll
+          for (int sl = 0; sl < 4; ++sl) {
+            const uint32_t x0 = w0[4 * rh + sl], x1 = w1[4 * rh + sl];
+            ra[2 * sl + 0] = cvt_bf16x2(deq8(x1, 0, cz[0], sf[0]), deq8(x0, 0, cz[0], sf[0]));
+            ra[2 * sl + 1] = cvt_bf16x2(deq8(x1, 1, cz[1], sf[1]), deq8(x0, 1, cz[1], sf[1]));
+            rb[2 * sl + 0] = cvt_bf16x2(deq8(x1, 2, cz[2], sf[2]), deq8(x0, 2, cz[2], sf[2]));
+            rb[2 * sl + 1] = cvt_bf16x2(deq8(x1, 3, cz[3], sf[3]), deq8(x0, 3, cz[3], sf[3]));
+          }
+          tmem_st_16x128b_x4(tmem_addr(a_tmem + 16 * rh, lane_base, 0), ra);
+          tmem_st_16x128b_x4(tmem_addr(a_tmem + 16 * rh, lane_base + 16, 0), rb);
         }
-        tmem_st_16x128b_x4(tmem_addr(a_tmem, lane_base, 0), ra);
-        tmem_st_16x128b_x4(tmem_addr(a_tmem, lane_base + 16, 0), rb);
       }
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(smem_u32(&bars.a_full[t]));
+      mbar_arrive(a_full_bar);
+      if (q == 0 && lane == 0 && team == 0) DX_TRACE(2, (u - u_begin) >> 2);
+      aph ^= 1u;
+      s += kAStages;
+      if (s >= SW) { s -= SW; ph ^= 1u; }
+      ku += kAStages;
+      while (ku >= U) { ku -= U; ++tile; }
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) DX_TRACE(7, 0);
   if (warp == 1) tmem_dealloc(tmem0, 512);
   if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, DXB_ERR_KERNEL_TIMEOUT);
 }
@@ -593,19 +714,21 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-static bool make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, uint64_t inner,
-                     uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner,
-                     uint32_t box_outer, CUtensorMapSwizzle sw) {
+// rank-2 or rank-3 tiled map; dims/box innermost first, strides in bytes for dims 1..rank-1.
+static bool make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int rank,
+                     const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                     CUtensorMapSwizzle sw) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {row_stride_bytes};
-  cuuint32_t box[2] = {box_inner, box_outer};
-  cuuint32_t es[2] = {1, 1};
-  return fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, es,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  cuuint64_t d[3], st[2];
+  cuuint32_t bx[3], es[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; bx[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) st[i] = strides_bytes[i];
+  return fn(m, dt, rank, const_cast<void*>(base), d, st, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+
+static long long* g_trace = nullptr;
 
 struct DeviceInfo {
   int sms = 0;
@@ -623,8 +746,8 @@ static DeviceInfo& device_info() {
 }
 
 struct Plan {
-  int NU, planes, rows, units_per_tile, tiles, total_units, stages, x_stage_bytes, ctas, max_slots,
-      nacc;
+  int NU, planes, rows, units_per_tile, tiles, total_units, stages, w_stages, x_stage_bytes, ctas,
+      max_slots, nacc;
   size_t smem_bytes;
 };
 
@@ -650,9 +773,19 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   pl.tiles = (N + kTileN - 1) / kTileN;
   pl.total_units = pl.units_per_tile * pl.tiles;
   pl.x_stage_bytes = pl.planes * pl.NU * 128;
-  int stages = kSmemBudget / (kWStage + pl.x_stage_bytes);
+  // Shared memory: a deep ring of small packed-weight stages (they come from HBM and
+  // need the most bytes in flight) and as many activation stages as still fit.
+  int w_stages = 12;
+  int stages = (kSmemBudget - w_stages * kWStage) / pl.x_stage_bytes;
+  if (stages < 3) {
+    w_stages = 8;
+    stages = (kSmemBudget - w_stages * kWStage) / pl.x_stage_bytes;
+  }
+  if (stages > 6) { stages = 6; w_stages = kMaxWStages; }
   pl.stages = stages > kMaxStages ? kMaxStages : stages;
-  pl.smem_bytes = static_cast<size_t>(pl.stages) * (kWStage + pl.x_stage_bytes) + 1024;
+  pl.w_stages = w_stages;
+  pl.smem_bytes = static_cast<size_t>(pl.w_stages) * kWStage +
+                  static_cast<size_t>(pl.stages) * pl.x_stage_bytes + 1024;
   int ctas = sms;
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (ctas > pl.total_units) ctas = pl.total_units;
@@ -686,22 +819,34 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
                       static_cast<size_t>(pl.tiles) * pl.max_slots * pl.NU * kTileN * sizeof(float);
   if (workspace == nullptr || workspace_bytes < need) return DXB_ERR_WORKSPACE;
 
-  CUtensorMap tq, tx, ts, tz;
-  const int rows = pl.rows;
-  bool ok = make_map(&tq, qw, CU_TENSOR_MAP_DATA_TYPE_UINT8, N, rows, N, kTileN, kUnitRows,
-                     CU_TENSOR_MAP_SWIZZLE_128B);
-  ok = ok && make_map(&tx, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, K, M, ldx * 2, 64, pl.NU,
-                      CU_TENSOR_MAP_SWIZZLE_128B);
-  ok = ok && make_map(&ts, scales, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, N, K / group,
-                      static_cast<uint64_t>(N) * 2, kTileN, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
-  if (HAS_ZERO)
-    ok = ok && make_map(&tz, zeros, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, N, K / group,
-                        static_cast<uint64_t>(N) * 2, kTileN, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
-  else
-    tz = ts;
+  CUtensorMap tq, tx;
+  bool ok;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(pl.rows)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(N)};
+    const uint32_t box[2] = {kTileN, kUnitRows};
+    ok = make_map(&tq, qw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, dims, strides, box,
+                  CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (BITS == 4) {
+    // X seen as [plane][token][k within the plane]: one box brings both k-slices of a unit.
+    const uint64_t dims[3] = {static_cast<uint64_t>(K / 2), static_cast<uint64_t>(M), 2};
+    const uint64_t strides[2] = {static_cast<uint64_t>(ldx) * 2, static_cast<uint64_t>(K / 2) * 2};
+    const uint32_t box[3] = {64, static_cast<uint32_t>(pl.NU), 2};
+    ok = ok && make_map(&tx, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldx) * 2};
+    const uint32_t box[2] = {64, static_cast<uint32_t>(pl.NU)};
+    ok = ok && make_map(&tx, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dims, strides, box,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+  }
   if (!ok) return DXB_ERR_TENSORMAP;
 
   WqParams p{};
+  p.scales = static_cast<const __nv_bfloat16*>(scales);
+  p.zeros = static_cast<const __nv_bfloat16*>(zeros);
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.ldo = ldo;
@@ -716,9 +861,12 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   p.total_units = pl.total_units;
   p.half_k = BITS == 4 ? K / 2 : 0;
   p.stages = pl.stages;
+  p.w_stages = pl.w_stages;
   p.x_stage_bytes = pl.x_stage_bytes;
   p.max_slots = pl.max_slots;
   p.nacc = pl.nacc;
+  { const char* e = getenv("DXB_DEBUG"); p.dbg = e ? atoi(e) : 0; }
+  p.trace = g_trace;
 
   auto kernel = wq_gemm_tc<BITS, HAS_ZERO>;
   static thread_local int attr_dev[4] = {-1, -1, -1, -1};
@@ -731,7 +879,7 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
       return DXB_ERR_CUDA;
     attr_dev[slot] = dev;
   }
-  kernel<<<pl.ctas, kThreads, pl.smem_bytes, stream>>>(tq, tx, ts, tz, p);
+  kernel<<<pl.ctas, kThreads, pl.smem_bytes, stream>>>(tq, tx, p);
   return cudaGetLastError() == cudaSuccess ? DXB_OK : DXB_ERR_CUDA;
 }
 
@@ -763,6 +911,8 @@ static int check_args(int bits, const void* x, long long ldx, const void* qw, co
 // =================================================================== C ABI ==
 extern "C" {
 
+void dxb_debug_set_trace(void* ptr) { dx::g_trace = static_cast<long long*>(ptr); }
+
 int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const void* scales,
                 const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
                 int group_size, void* workspace, size_t workspace_bytes, int max_ctas,
@@ -775,7 +925,10 @@ int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const
   const bool aligned = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) &&
                        (reinterpret_cast<uintptr_t>(qweight) % 16 == 0) &&
                        (reinterpret_cast<uintptr_t>(scales) % 16 == 0) &&
-                       (zeros == nullptr || reinterpret_cast<uintptr_t>(zeros) % 16 == 0);
+                       (zeros == nullptr || reinterpret_cast<uintptr_t>(zeros) % 16 == 0) &&
+                       (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 8 == 0) &&
+                       (reinterpret_cast<uintptr_t>(out) % 8 == 0) && (ldo % 4 == 0) &&
+                       (bits != 4 || (K / 2) % 8 == 0);
   // Token blocks of at most 256 rows per launch (128 keeps two accumulators in TMEM).
   const int chunk = M <= 256 ? M : 128;
   for (int m0 = 0; m0 < M; m0 += chunk) {
