@@ -149,16 +149,18 @@ __host__ __device__ inline int owner_of(long long u, long long total, long long 
 
 // ----------------------------------------------------------------- the kernel
 // Barrier slots in shared memory.
-constexpr int kBarFullW = 0, kBarEmptyW = 16, kBarFullX = 32, kBarEmptyX = 40, kBarAFull = 48,
-              kBarAEmpty = 52, kBarAccFull = 56, kBarAccEmpty = 58, kNumBars = 60;
+// ready[t]: unit slot t has its activations in shared memory (TMA bytes) AND its
+// dequantised weights in TMEM (128 arrivals of one team); free[t]: the MMAs that
+// read slot t are done (one tcgen05.commit), so both may be overwritten.
+constexpr int kBarFullW = 0, kBarEmptyW = 16, kBarReady = 32, kBarFree = 36, kBarAccFull = 40,
+              kBarAccEmpty = 42, kNumBars = 44;
 
 __device__ __forceinline__ uint32_t bar_count(int i) {
-  if (i < kBarEmptyW) return 1;                 // full_w: producer's expect_tx
-  if (i < kBarFullX) return kDequantThreads;    // empty_w: every dequant thread
-  if (i < kBarAFull) return 1;                  // full_x (expect_tx), empty_x (commit)
-  if (i < kBarAEmpty) return kDequantThreads;   // a_full
-  if (i < kBarAccEmpty) return 1;               // a_empty, acc_full (commit)
-  return kEpilogueThreads;                      // acc_empty
+  if (i < kBarEmptyW) return 1;                    // full_w: producer's expect_tx
+  if (i < kBarReady) return kDequantThreads;       // empty_w: one dequant team
+  if (i < kBarFree) return kDequantThreads + 1;    // ready: team + activation producer
+  if (i < kBarAccEmpty) return 1;                  // free, acc_full: one tcgen05.commit
+  return kEpilogueThreads;                         // acc_empty
 }
 
 template <int BITS, bool HAS_ZERO>
@@ -181,7 +183,6 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const uint32_t bar0 = smem_u32(bars);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int S = p.stages;
   const int SW = p.w_stages;
 
   if (warp == 3) {
@@ -231,6 +232,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           const uint32_t fw = bar0 + 8 * (kBarFullW + s);
           mbar_expect_tx(fw, kQBytes);
           tma_load_2d(w_ring + s * kWStage, &tm_q, fw, tile * kTileN, ku * kUnitRows);
+          DX_TRACE(5, issued);
         }
         __syncwarp();
         ++issued;
@@ -249,33 +251,33 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   } else if (warp == 2) {
     // ============================================== TMA producer: activations
     {
-      int ku = ku_begin, s = 0;
+      int ku = ku_begin, t = 0;
       uint32_t ph = 0;
       int issued = 0;
       bool ok = true;
       const uint32_t x_bytes = p.x_stage_bytes;
       for (int u = u_begin; u < u_end; ++u) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarEmptyX + s), ph ^ 1u, abortp));
+        ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarFree + t), ph ^ 1u, abortp));
         if (!ok) break;
         if (elect_one()) {
-          const uint32_t fx = bar0 + 8 * (kBarFullX + s);
-          mbar_expect_tx(fx, x_bytes);
+          const uint32_t rb = bar0 + 8 * (kBarReady + t);
+          mbar_expect_tx(rb, x_bytes);
           if (BITS == 4)
-            tma_load_3d(x_ring + s * p.x_stage_bytes, &tm_x, fx, ku * kUnitRows, 0, 0);
+            tma_load_3d(x_ring + t * p.x_stage_bytes, &tm_x, rb, ku * kUnitRows, 0, 0);
           else
-            tma_load_2d(x_ring + s * p.x_stage_bytes, &tm_x, fx, ku * kUnitRows, 0);
+            tma_load_2d(x_ring + t * p.x_stage_bytes, &tm_x, rb, ku * kUnitRows, 0);
         }
         __syncwarp();
         ++issued;
-        if (++s == S) { s = 0; ph ^= 1u; }
+        if (++t == kAStages) { t = 0; ph ^= 1u; }
         if (++ku == U) ku = 0;
       }
       if (!ok && lane == 0) {
-        for (int j = (issued > S ? issued - S : 0); j < issued; ++j)
-          for (int spin = 0; spin < 200000; ++spin)
-            if (mbar_try_wait(bar0 + 8 * (kBarFullX + j % S), static_cast<uint32_t>(j / S) & 1u))
-              break;
+        // Leaving early: give copies already issued time to land before the CTA exits.
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {}
       }
+      (void)issued;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -287,8 +289,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const uint64_t xdesc0 = smem_desc_kmajor_sw128(x_ring);
       const uint32_t x_stage16 = static_cast<uint32_t>(p.x_stage_bytes) >> 4;
       const uint32_t plane16 = static_cast<uint32_t>(p.NU * 128) >> 4;
-      int s = 0, t = 0, b = 0;
-      uint32_t ph = 0, aph = 0, accph = 0;
+      int t = 0, b = 0;
+      uint32_t ph = 0, accph = 0;
       uint64_t xd = xdesc0;
       uint32_t a_tmem = tmem0 + kACol0;
       bool ok = true;
@@ -298,12 +300,9 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const int nun = left < (U - ku0) ? left : (U - ku0);
         ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarAccEmpty + b), accph ^ 1u, abortp));
         if (!ok) break;
-        tc_fence_after();
         const uint32_t d_tmem = tmem0 + b * p.NU;
         for (int i = 0; i < nun; ++i) {
-          ok = mbar_wait(bar0 + 8 * (kBarFullX + s), ph, abortp);
-          ok = mbar_wait(bar0 + 8 * (kBarAFull + t), aph, abortp) && ok;
-          ok = __all_sync(0xffffffffu, ok);
+          ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarReady + t), ph, abortp));
           if (!ok) break;
           tc_fence_after();
           if (elect_one()) {
@@ -319,23 +318,21 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
               for (int kk = 0; kk < 4; ++kk)
                 mma_ts(d_tmem, a_tmem + 32 + kk * 8, xd + plane16 + kk * 2, idesc, 1u);
             }
-            tc_commit(bar0 + 8 * (kBarAEmpty + t));
-            tc_commit(bar0 + 8 * (kBarEmptyX + s));
+            tc_commit(bar0 + 8 * (kBarFree + t));
           }
           __syncwarp();
           if (lane == 0) DX_TRACE(3, done);
           ++done;
           xd += x_stage16;
-          if (++s == S) { s = 0; ph ^= 1u; xd = xdesc0; }
           a_tmem += A_STAGE_COLS;
-          if (++t == kAStages) { t = 0; aph ^= 1u; a_tmem = tmem0 + kACol0; }
+          if (++t == kAStages) { t = 0; ph ^= 1u; xd = xdesc0; a_tmem = tmem0 + kACol0; }
         }
         if (!ok) break;
         if (elect_one()) tc_commit(bar0 + 8 * (kBarAccFull + b));
         __syncwarp();
         u += nun;
         ku0 = 0;
-        if (++b == p.nacc) { b = 0; accph ^= 1u; }
+        if (++b == 2) { b = 0; accph ^= 1u; }
       }
     }
     __syncwarp();
@@ -487,7 +484,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       u += nun;
       ku0 = 0;
       ++tile;
-      if (++b == p.nacc) { b = 0; accph ^= 1u; }
+      if (++b == 2) { b = 0; accph ^= 1u; }
     }
   } else if (warp >= 8) {
     // ========================================================== dequant ====
@@ -514,8 +511,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const uint2* sc_ptr = reinterpret_cast<const uint2*>(p.scales);
     const uint2* zr_ptr = reinterpret_cast<const uint2*>(p.zeros);
     const uint32_t a_tmem = tmem0 + kACol0 + team * A_STAGE_COLS;
-    const uint32_t a_full_bar = bar0 + 8 * (kBarAFull + team);
-    const uint32_t a_empty_bar = bar0 + 8 * (kBarAEmpty + team);
+    const uint32_t a_full_bar = bar0 + 8 * (kBarReady + team);
+    const uint32_t a_empty_bar = bar0 + 8 * (kBarFree + team);
 
     // cursor of this team's current unit
     int u = u_begin + team;
@@ -525,21 +522,32 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     uint32_t ph = 0;
     uint32_t aph = 0;
     bool ok = true;
-    for (; u < u_end; u += kAStages) {
-      // scales / zero points for this unit, straight from global (L2-resident)
-      uint2 sc[PLANES], zr[PLANES];
-      {
-        const int n = tile * kTileN + n_local;
+    // Scales / zero points come straight from global memory (they are tiny and stay in
+    // L2), fetched one team-unit ahead so the load latency is never waited for.
+    uint2 sc[PLANES], zr[PLANES], sc_nx[PLANES], zr_nx[PLANES];
+    auto load_sz = [&](int tile_, int ku_, uint2 (&s_out)[PLANES], uint2 (&z_out)[PLANES]) {
+      const int n = tile_ * kTileN + n_local;
+      const bool in = n < p.N && tile_ < p.tiles;
 #pragma unroll
-        for (int pl = 0; pl < PLANES; ++pl) {
-          const int grp = (ku + pl * half_units) / group_units;
-          const long long idx = (static_cast<long long>(grp) * p.N + n) >> 2;
-          sc[pl] = n < p.N ? __ldg(sc_ptr + idx) : make_uint2(0u, 0u);
-          if (HAS_ZERO) zr[pl] = n < p.N ? __ldg(zr_ptr + idx) : make_uint2(0u, 0u);
-        }
+      for (int pl = 0; pl < PLANES; ++pl) {
+        const int grp = (ku_ + pl * half_units) / group_units;
+        const long long idx = (static_cast<long long>(grp) * p.N + n) >> 2;
+        s_out[pl] = in ? __ldg(sc_ptr + idx) : make_uint2(0u, 0u);
+        if (HAS_ZERO) z_out[pl] = in ? __ldg(zr_ptr + idx) : make_uint2(0u, 0u);
+      }
+    };
+    if (u < u_end) load_sz(tile, ku, sc_nx, zr_nx);
+    for (; u < u_end; u += kAStages) {
+#pragma unroll
+      for (int pl = 0; pl < PLANES; ++pl) { sc[pl] = sc_nx[pl]; if (HAS_ZERO) zr[pl] = zr_nx[pl]; }
+      {
+        int ku_n = ku + kAStages, tile_n = tile;
+        while (ku_n >= U) { ku_n -= U; ++tile_n; }
+        if (u + kAStages < u_end) load_sz(tile_n, ku_n, sc_nx, zr_nx);
       }
       ok = mbar_wait(bar0 + 8 * (kBarFullW + s), ph, abortp);
       if (!ok) break;
+      if (q == 0 && lane == 0) DX_TRACE(4, (u - u_begin));
       const uint32_t wsrc = w_ring + s * kWStage;
       uint32_t w0[8], w1[8];
 #pragma unroll
@@ -550,6 +558,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       mbar_arrive(bar0 + 8 * (kBarEmptyW + s));  // packed stage is in registers now
       ok = mbar_wait(a_empty_bar, aph ^ 1u, abortp);
       if (!ok) break;
+      if (q == 0 && lane == 0) DX_TRACE(6, (u - u_begin));
       tc_fence_after();
       if (BITS == 4) {
 #pragma unroll
@@ -607,7 +616,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(a_full_bar);
-      if (q == 0 && lane == 0 && team == 0) DX_TRACE(2, (u - u_begin) >> 2);
+      if (q == 0 && lane == 0) DX_TRACE(2, (u - u_begin));
       aph ^= 1u;
       s += kAStages;
       if (s >= SW) { s -= SW; ph ^= 1u; }
@@ -753,7 +762,7 @@ struct Plan {
 
 // Shapes the tensor-core kernel takes.  Everything else goes to wq_gemm_simt.
 static bool tc_supported(int M, int N, int K, int group, int bits) {
-  if (M < 1 || M > 256) return false;
+  if (M < 1 || M > 128) return false;
   if (N % 16 || N < 16) return false;
   const int rows = bits == 4 ? K / 2 : K;
   if (bits == 4 && (K % 2)) return false;
@@ -773,16 +782,14 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   pl.tiles = (N + kTileN - 1) / kTileN;
   pl.total_units = pl.units_per_tile * pl.tiles;
   pl.x_stage_bytes = pl.planes * pl.NU * 128;
-  // Shared memory: a deep ring of small packed-weight stages (they come from HBM and
-  // need the most bytes in flight) and as many activation stages as still fit.
-  int w_stages = 12;
-  int stages = (kSmemBudget - w_stages * kWStage) / pl.x_stage_bytes;
-  if (stages < 3) {
-    w_stages = 8;
-    stages = (kSmemBudget - w_stages * kWStage) / pl.x_stage_bytes;
-  }
-  if (stages > 6) { stages = 6; w_stages = kMaxWStages; }
-  pl.stages = stages > kMaxStages ? kMaxStages : stages;
+  // Shared memory: four activation stages (one per unit slot, like the TMEM ring) and
+  // as deep a ring of packed-weight stages as still fits: those come from HBM and
+  // need the most bytes in flight.  The depth is a multiple of four so that every
+  // stage is only ever used by one dequant team, in order.
+  pl.stages = kAStages;
+  int w_stages = (kSmemBudget - kAStages * pl.x_stage_bytes) / kWStage;
+  w_stages = (w_stages / kAStages) * kAStages;
+  if (w_stages > kMaxWStages) w_stages = kMaxWStages;
   pl.w_stages = w_stages;
   pl.smem_bytes = static_cast<size_t>(pl.w_stages) * kWStage +
                   static_cast<size_t>(pl.stages) * pl.x_stage_bytes + 1024;
@@ -790,7 +797,7 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (ctas > pl.total_units) ctas = pl.total_units;
   pl.ctas = ctas;
-  pl.nacc = pl.NU <= 128 ? 2 : 1;
+  pl.nacc = 2;
   int max_slots = 1;
   for (int t = 0; t < pl.tiles; ++t) {
     const long long u0 = static_cast<long long>(t) * pl.units_per_tile;
@@ -814,7 +821,7 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
                      cudaStream_t stream) {
   DeviceInfo& di = device_info();
   const Plan pl = make_plan(M, N, K, BITS, di.sms, max_ctas);
-  if (pl.stages < 2) return DXB_ERR_UNSUPPORTED;
+  if (pl.w_stages < kAStages) return DXB_ERR_UNSUPPORTED;
   const size_t need = kStatusBytes + counters_bytes(pl.tiles) +
                       static_cast<size_t>(pl.tiles) * pl.max_slots * pl.NU * kTileN * sizeof(float);
   if (workspace == nullptr || workspace_bytes < need) return DXB_ERR_WORKSPACE;
@@ -929,8 +936,8 @@ int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const
                        (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 8 == 0) &&
                        (reinterpret_cast<uintptr_t>(out) % 8 == 0) && (ldo % 4 == 0) &&
                        (bits != 4 || (K / 2) % 8 == 0);
-  // Token blocks of at most 256 rows per launch (128 keeps two accumulators in TMEM).
-  const int chunk = M <= 256 ? M : 128;
+  // Token blocks of at most 128 rows per launch (the UMMA N of one accumulator).
+  const int chunk = M <= 128 ? M : 128;
   for (int m0 = 0; m0 < M; m0 += chunk) {
     const int mc = (M - m0) < chunk ? (M - m0) : chunk;
     const char* xc = static_cast<const char*>(x) + static_cast<long long>(m0) * ldx * 2;
@@ -974,7 +981,7 @@ int dxb_w8a16(const void* x, int64_t ldx, const void* qweight, const void* scale
 size_t dxb_workspace_bytes(int M, int N, int K, int bits) {
   using namespace dx;
   if (M <= 0 || N <= 0 || K <= 0 || (bits != 4 && bits != 8)) return kStatusBytes;
-  const int mc = M <= 256 ? M : 128;
+  const int mc = M <= 128 ? M : 128;
   const int rows = bits == 4 ? K / 2 : K;
   if (rows < kUnitRows) return kStatusBytes;
   DeviceInfo& di = device_info();
@@ -1006,7 +1013,7 @@ int dxb_dequantize(const void* qweight, const void* scales, const void* zeros, v
 }
 
 int dxb_uses_tensor_cores(int M, int N, int K, int group_size, int bits) {
-  const int mc = M <= 256 ? M : 128;
+  const int mc = M <= 128 ? M : 128;
   return dx::tc_supported(mc, N, K, group_size, bits) ? 1 : 0;
 }
 
