@@ -49,27 +49,38 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Same test, but the hardware may park the thread for up to `hint_ns` until the
+// phase completes, instead of returning at once: a waiting warp then costs no
+// issue slots and is woken by the barrier itself.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity,
+                                                     uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 
-// Upper bound of one wait, in SM clock cycles (about one second at 2 GHz).
-constexpr long long kWaitCycles = 2000000000LL;
+// Upper bound of one wait: kWaitTries parked attempts of kWaitHintNs each (about
+// one second in all, whatever the clock).
+constexpr uint32_t kWaitHintNs = 1000000u;
+constexpr uint32_t kWaitTries = 1000u;
 
 // Bounded wait on an mbarrier phase.  `abort_flag` is a CTA-shared word: once
 // any role gives up it is set, and every other wait in the CTA returns false
 // at its next poll so the whole CTA drains to its tear-down.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  uint32_t spins = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0xff) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
+  for (uint32_t tries = 0; tries < kWaitTries; ++tries) {
+    if (mbar_try_wait_parked(bar, parity, kWaitHintNs)) return true;
+    if (*abort_flag) return false;
   }
+  *abort_flag = 1;
+  return false;
 }
 
 // --------------------------------------------------------------------- TMA --

@@ -41,7 +41,11 @@
 #include "sm100_ptx.cuh"
 
 namespace dx {
+#ifdef DXB_TRACE
 #define DX_TRACE(role, i) do { if (p.trace && (i) < 32) p.trace[(static_cast<long long>(blockIdx.x) * 8 + (role)) * 32 + (i)] = clock64() - t_start; } while (0)
+#else
+#define DX_TRACE(role, i) do { } while (0)
+#endif
 
 // ------------------------------------------------------------------ constants
 constexpr int kTileN = 128;      // weight columns per tile (UMMA M)
@@ -79,6 +83,7 @@ struct WqParams {
   int x_stage_bytes;   // planes * NU * 128
   int max_slots;       // partial slots reserved per tile
   int nacc;            // accumulator buffers in TMEM (2 when NU <= 128)
+  int group_shift;     // log2(group / 64) when that is a power of two, else -1
   int dbg;
   long long* trace;
 };
@@ -232,7 +237,6 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           const uint32_t fw = bar0 + 8 * (kBarFullW + s);
           mbar_expect_tx(fw, kQBytes);
           tma_load_2d(w_ring + s * kWStage, &tm_q, fw, tile * kTileN, ku * kUnitRows);
-          DX_TRACE(5, issued);
         }
         __syncwarp();
         ++issued;
@@ -302,8 +306,10 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (!ok) break;
         const uint32_t d_tmem = tmem0 + b * p.NU;
         for (int i = 0; i < nun; ++i) {
+          if (lane == 0) DX_TRACE(0, done);
           ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarReady + t), ph, abortp));
           if (!ok) break;
+          if (lane == 0) DX_TRACE(1, done);
           tc_fence_after();
           if (elect_one()) {
             if (i == 0) {
@@ -318,6 +324,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
               for (int kk = 0; kk < 4; ++kk)
                 mma_ts(d_tmem, a_tmem + 32 + kk * 8, xd + plane16 + kk * 2, idesc, 1u);
             }
+            DX_TRACE(5, done);
             tc_commit(bar0 + 8 * (kBarFree + t));
           }
           __syncwarp();
@@ -525,13 +532,15 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // Scales / zero points come straight from global memory (they are tiny and stay in
     // L2), fetched one team-unit ahead so the load latency is never waited for.
     uint2 sc[PLANES], zr[PLANES], sc_nx[PLANES], zr_nx[PLANES];
+    const int n4_stride = p.N >> 2;  // uint2 (4 x bf16) elements per scale row
     auto load_sz = [&](int tile_, int ku_, uint2 (&s_out)[PLANES], uint2 (&z_out)[PLANES]) {
       const int n = tile_ * kTileN + n_local;
       const bool in = n < p.N && tile_ < p.tiles;
 #pragma unroll
       for (int pl = 0; pl < PLANES; ++pl) {
-        const int grp = (ku_ + pl * half_units) / group_units;
-        const long long idx = (static_cast<long long>(grp) * p.N + n) >> 2;
+        const int kunit = ku_ + pl * half_units;
+        const int grp = p.group_shift >= 0 ? (kunit >> p.group_shift) : (kunit / group_units);
+        const int idx = grp * n4_stride + (n >> 2);
         s_out[pl] = in ? __ldg(sc_ptr + idx) : make_uint2(0u, 0u);
         if (HAS_ZERO) z_out[pl] = in ? __ldg(zr_ptr + idx) : make_uint2(0u, 0u);
       }
@@ -872,6 +881,12 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   p.x_stage_bytes = pl.x_stage_bytes;
   p.max_slots = pl.max_slots;
   p.nacc = pl.nacc;
+  {
+    const int gu = group / kUnitRows;
+    int sh = -1;
+    for (int b = 0; b < 20; ++b) if ((1 << b) == gu) sh = b;
+    p.group_shift = sh;
+  }
   { const char* e = getenv("DXB_DEBUG"); p.dbg = e ? atoi(e) : 0; }
   p.trace = g_trace;
 
