@@ -84,8 +84,7 @@ struct WqParams {
   int max_slots;       // partial slots reserved per tile
   int nacc;            // accumulator buffers in TMEM (2 when NU <= 128)
   int group_shift;     // log2(group / 64) when that is a power of two, else -1
-  int dbg;
-  long long* trace;
+  long long* trace;    // only used when built with -DDXB_TRACE
 };
 
 // -------------------------------------------------------------- dequant math
@@ -887,7 +886,6 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
     for (int b = 0; b < 20; ++b) if ((1 << b) == gu) sh = b;
     p.group_shift = sh;
   }
-  { const char* e = getenv("DXB_DEBUG"); p.dbg = e ? atoi(e) : 0; }
   p.trace = g_trace;
 
   auto kernel = wq_gemm_tc<BITS, HAS_ZERO>;
@@ -933,7 +931,9 @@ static int check_args(int bits, const void* x, long long ldx, const void* qw, co
 // =================================================================== C ABI ==
 extern "C" {
 
+#ifdef DXB_TRACE
 void dxb_debug_set_trace(void* ptr) { dx::g_trace = static_cast<long long*>(ptr); }
+#endif
 
 int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const void* scales,
                 const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,

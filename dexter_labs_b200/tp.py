@@ -1,0 +1,264 @@
+"""Tensor-parallel sharding of packed weights and the linear-layer set built on it.
+
+The reference is a single-device engine (its README states multi-GPU is out of
+scope), so nothing here has a counterpart there; the unsharded reference result
+is the oracle.  What it has to respect is the reference's packed layout
+(``python/dexter/quant.py:62-133``):
+
+* column-parallel (QKV, cross Q/K/V, FFN-up): every output column owns one
+  column of ``qweight`` / ``scales`` / ``zeros`` / ``bias``, so a shard is a plain
+  slice along N -- bit-identical to quantising the sliced weight.
+* row-parallel (O, FFN-down): a packed int4 byte row carries logical rows ``i``
+  and ``i + K/2``, so slicing packed rows would hand a rank two disjoint K ranges.
+  Instead the weight is cut in the LOGICAL domain on whole quantisation groups
+  (group statistics are per group and column, so this is again bit-identical to
+  quantising the slice) and every shard is re-packed split-half on its own.
+  Each rank then multiplies its contiguous slice of the activation columns and
+  the partial products are summed across ranks; the bias rides on rank 0 only.
+
+``LayerSet`` strings the ten linears of a DiT block (self q/k/v/o, cross
+q/k/v/o, FFN up/down; shapes from ``python/dexter/models/dreamzero/config.py``
+and ``model.py:148-151,204-207,260-261``) into column->row pairs with one
+reduce-scatter + all-gather (or all-reduce) after every row-parallel linear.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from .quant import QuantizedWeight, pack_nibbles, quantize
+
+__all__ = ["group_bounds", "split_columns", "split_rows", "ShardedLinear", "LayerSet", "PRESETS",
+           "unpack_nibbles"]
+
+# name -> (dim, ffn_dim, blocks); python/dexter/models/dreamzero/config.py:182-219
+PRESETS: Dict[str, Tuple[int, int, int]] = {"5b": (3072, 14336, 30), "14b": (5120, 13824, 40)}
+
+GemmFn = Callable[[torch.Tensor, QuantizedWeight], torch.Tensor]
+
+
+def unpack_nibbles(qweight: torch.Tensor) -> torch.Tensor:
+    """``[K/2, N]`` packed bytes -> ``[K, N]`` values 0..15 (low nibbles first)."""
+    return torch.cat((qweight & 0x0F, (qweight >> 4) & 0x0F), dim=0)
+
+
+def group_bounds(num_groups: int, rank: int, world: int) -> Tuple[int, int]:
+    """Whole groups ``[g0, g1)`` owned by ``rank``; sizes differ by at most one group."""
+    base, extra = divmod(num_groups, world)
+    g0 = rank * base + min(rank, extra)
+    return g0, g0 + base + (1 if rank < extra else 0)
+
+
+def split_columns(qw: QuantizedWeight, rank: int, world: int) -> QuantizedWeight:
+    """Column-parallel shard: columns ``[rank*N/world, (rank+1)*N/world)`` of every tensor."""
+    k, n = qw.shape
+    if n % world:
+        raise ValueError(f"N={n} does not split into {world} column shards")
+    n0, n1 = rank * n // world, (rank + 1) * n // world
+
+    def cut(t):
+        return None if t is None else t[..., n0:n1].contiguous()
+
+    return QuantizedWeight(cut(qw.qweight), cut(qw.scales), cut(qw.zeros), cut(qw.bias),
+                           qw.group_size, qw.bits, (k, n1 - n0))
+
+
+def split_rows(qw: QuantizedWeight, rank: int, world: int) -> Tuple[QuantizedWeight, Tuple[int, int]]:
+    """Row-parallel shard on whole groups, re-packed; returns it with its K range ``(k0, k1)``."""
+    k, n = qw.shape
+    g = qw.group_size
+    if k // g < world:
+        raise ValueError(f"K={k} has {k // g} group(s) of {g}: fewer than the {world} ranks")
+    g0, g1 = group_bounds(k // g, rank, world)
+    k0, k1 = g0 * g, g1 * g
+    if qw.bits == 4:
+        logical = unpack_nibbles(qw.qweight)[k0:k1]
+        if (k1 - k0) % 2:
+            raise ValueError("an int4 shard needs an even number of rows")
+        packed = pack_nibbles(logical)
+    else:
+        packed = qw.qweight[k0:k1].contiguous()
+    shard = QuantizedWeight(packed, qw.scales[g0:g1].contiguous(),
+                            None if qw.zeros is None else qw.zeros[g0:g1].contiguous(),
+                            qw.bias if rank == 0 else None, g, qw.bits, (k1 - k0, n))
+    return shard, (k0, k1)
+
+
+@dataclass
+class ShardedLinear:
+    """One linear of the set on one rank."""
+
+    name: str
+    kind: str  # "column" | "row"
+    weight: QuantizedWeight
+    k_range: Tuple[int, int]  # activation columns this rank consumes
+    full_shape: Tuple[int, int]  # unsharded (K, N)
+
+    @property
+    def weight_bytes(self) -> int:
+        return self.weight.nbytes
+
+    def flops(self, m: int) -> int:
+        k, n = self.weight.shape
+        return 2 * m * k * n
+
+
+def _default_gemm(x: torch.Tensor, w: QuantizedWeight) -> torch.Tensor:
+    from . import ops
+
+    fn = ops.w4a16 if w.bits == 4 else ops.w8a16
+    return fn(x, w.qweight, w.scales, w.zeros, w.bias, w.group_size)
+
+
+# (name, input, kind): the ten linears of one DiT block in execution order
+_BLOCK_PLAN = (
+    ("self_q", "dim", "column"), ("self_k", "dim", "column"), ("self_v", "dim", "column"),
+    ("self_o", "dim", "row"),
+    ("cross_q", "dim", "column"), ("cross_k", "dim", "column"), ("cross_v", "dim", "column"),
+    ("cross_o", "dim", "row"),
+    ("ffn_up", "dim", "column"), ("ffn_down", "ffn", "row"),
+)
+
+
+@dataclass
+class LayerSet:
+    """The quantised linears of ``blocks`` DiT blocks, sharded for one rank.
+
+    ``forward`` runs them as column->row pairs.  There is no attention, norm or
+    activation function between them (those are other ops of the reference, not part
+    of this path): the column-parallel output that would feed attention goes
+    straight into the row-parallel projection, which keeps every GEMM's shape,
+    bytes and flops exactly those of the model.
+    """
+
+    dim: int
+    ffn_dim: int
+    blocks: int
+    rank: int = 0
+    world: int = 1
+    bits: int = 4
+    group_size: int = 128
+    collective: str = "rs_ag"  # "rs_ag" | "all_reduce"
+    layers: List[List[ShardedLinear]] = field(default_factory=list)
+    gemm: GemmFn = _default_gemm
+    process_group: Optional[object] = None
+    _pad: Dict[Tuple[int, int], torch.Tensor] = field(default_factory=dict)
+
+    # ------------------------------------------------------------------ build
+    @classmethod
+    def build(cls, preset: str, *, blocks: Optional[int] = None, rank: int = 0, world: int = 1,
+              bits: int = 4, group_size: int = 128, symmetric: bool = True, bias: bool = True,
+              device="cuda", seed: int = 0, collective: str = "rs_ag", gemm: GemmFn = _default_gemm,
+              process_group=None, weight_std: float = 0.02) -> "LayerSet":
+        dim, ffn, nblocks = PRESETS[preset]
+        nblocks = blocks if blocks is not None else nblocks
+        self = cls(dim, ffn, nblocks, rank, world, bits, group_size, collective, [], gemm,
+                   process_group)
+        for blk in range(nblocks):
+            row: List[ShardedLinear] = []
+            for idx, (name, src, kind) in enumerate(_BLOCK_PLAN):
+                k = dim if src == "dim" else ffn
+                n = ffn if name == "ffn_up" else dim
+                gen = torch.Generator(device="cpu").manual_seed(seed + 1000 * blk + idx)
+                w = (torch.randn(n, k, generator=gen) * weight_std).to(torch.bfloat16).to(device)
+                b = (torch.randn(n, generator=gen) * 0.1).to(torch.bfloat16).to(device) if bias else None
+                g = group_size if group_size > 0 else k
+                full = quantize(w, bits=bits, group_size=g, bias=b, symmetric=symmetric)
+                row.append(self.shard(name, kind, full))
+                del w, full
+            self.layers.append(row)
+        return self
+
+    def shard(self, name: str, kind: str, full: QuantizedWeight) -> ShardedLinear:
+        k, n = full.shape
+        if self.world == 1:
+            return ShardedLinear(name, kind, full, (0, k), (k, n))
+        if kind == "column":
+            return ShardedLinear(name, kind, split_columns(full, self.rank, self.world), (0, k), (k, n))
+        part, k_range = split_rows(full, self.rank, self.world)
+        return ShardedLinear(name, kind, part, k_range, (k, n))
+
+    # ------------------------------------------------------------------ stats
+    @property
+    def num_gemms(self) -> int:
+        return sum(len(r) for r in self.layers)
+
+    @property
+    def weight_bytes(self) -> int:
+        return sum(l.weight_bytes for r in self.layers for l in r)
+
+    def flops(self, m: int) -> int:
+        return sum(l.flops(m) for r in self.layers for l in r)
+
+    # ---------------------------------------------------------------- forward
+    def _reduce(self, partial: torch.Tensor) -> torch.Tensor:
+        """Sum the row-parallel partial products over ranks; every rank gets the full result."""
+        if self.world == 1:
+            return partial
+        import torch.distributed as dist
+
+        if self.collective == "all_reduce":
+            dist.all_reduce(partial, group=self.process_group)
+            return partial
+        m, n = partial.shape
+        rows = -(-m // self.world)  # token rows per rank, padded so the scatter is even
+        key = (rows * self.world, n)
+        buf = self._pad.get(key)
+        if buf is None or buf.device != partial.device:
+            buf = torch.zeros(key, dtype=partial.dtype, device=partial.device)
+            self._pad[key] = buf
+        buf[:m].copy_(partial)
+        mine = torch.empty((rows, n), dtype=partial.dtype, device=partial.device)
+        dist.reduce_scatter_tensor(mine, buf, group=self.process_group)
+        out = torch.empty_like(buf)
+        dist.all_gather_into_tensor(out, mine, group=self.process_group)
+        return out[:m]
+
+    def _local_cols(self, full_cols: int) -> Tuple[int, int]:
+        return self.rank * full_cols // self.world, (self.rank + 1) * full_cols // self.world
+
+    def block_forward(self, blk: int, x: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
+        """x, ctx: ``[M, dim]`` replicated on every rank; returns the new replicated x."""
+        L = {l.name: l for l in self.layers[blk]}
+        g = self.gemm
+        # self attention: q, k, v column-parallel; the v shard stands in for the attention output
+        g(x, L["self_q"].weight)
+        g(x, L["self_k"].weight)
+        v = g(x, L["self_v"].weight)
+        x = self._reduce(g(self._row_input(v, L["self_o"]), L["self_o"].weight))
+        # cross attention: q on x, k and v on the context
+        g(x, L["cross_q"].weight)
+        g(ctx, L["cross_k"].weight)
+        cv = g(ctx, L["cross_v"].weight)
+        x = self._reduce(g(self._row_input(cv, L["cross_o"]), L["cross_o"].weight))
+        # FFN
+        h = g(x, L["ffn_up"].weight)
+        x = self._reduce(g(self._row_input(h, L["ffn_down"]), L["ffn_down"].weight))
+        return x
+
+    def _row_input(self, col_out: torch.Tensor, row_layer: ShardedLinear) -> torch.Tensor:
+        """Activation slice a row-parallel linear consumes.
+
+        With even column shards the column-parallel output of this rank IS that
+        slice.  When the row cut (whole groups) does not coincide with the column
+        cut, the slice is gathered first.
+        """
+        k0, k1 = row_layer.k_range
+        if self.world == 1:
+            return col_out
+        c0, c1 = self._local_cols(row_layer.full_shape[0])
+        if (c0, c1) == (k0, k1):
+            return col_out
+        import torch.distributed as dist
+
+        parts = [torch.empty_like(col_out) for _ in range(self.world)]
+        dist.all_gather(parts, col_out.contiguous(), group=self.process_group)
+        return torch.cat(parts, dim=-1)[:, k0:k1].contiguous()
+
+    def forward(self, x: torch.Tensor, ctx: Optional[torch.Tensor] = None) -> torch.Tensor:
+        ctx = x if ctx is None else ctx
+        for blk in range(self.blocks):
+            x = self.block_forward(blk, x, ctx)
+        return x

@@ -1,0 +1,55 @@
+"""Tensor-parallel layer set over NCCL on 2 GPUs (skipped with fewer).  -m gpu."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT  # noqa: F401
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from dexter_labs_b200 import tp
+
+        ls = tp.LayerSet.build("5b", blocks=1, rank=rank, world=world, seed=3, device=f"cuda:{rank}")
+        torch.manual_seed(1)
+        x = torch.randn(83, 3072).to(torch.bfloat16).cuda()
+        ctx = torch.randn(83, 3072).to(torch.bfloat16).cuda()
+        y = ls.forward(x, ctx)
+        torch.cuda.synchronize()
+        results[rank] = y.float().cpu().numpy()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_layer_set_matches_one_gpu(b200_lib):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from dexter_labs_b200 import tp
+
+    single = tp.LayerSet.build("5b", blocks=1, seed=3)
+    torch.manual_seed(1)
+    x = torch.randn(83, 3072).to(torch.bfloat16).cuda()
+    ctx = torch.randn(83, 3072).to(torch.bfloat16).cuda()
+    want = single.forward(x, ctx).float().cpu().numpy()
+    world = 2
+    results = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    for rank in range(world):
+        e = np.abs(results[rank] - want).max() / max(np.abs(want).max(), 1e-6)
+        assert e < 1e-2, (rank, e)

@@ -1,0 +1,158 @@
+"""Tensor-parallel sharding of packed weights: CPU checks, including 2 gloo ranks.
+
+The sharded path has no counterpart in the reference (a single-device engine);
+its oracle is the unsharded result computed by the CPU oracle.
+"""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT  # noqa: F401  (puts the repo root on sys.path)
+
+
+def bits(t):
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def oracle_gemm(x, w):
+    from oracle import wq_oracle
+
+    return wq_oracle.torch_wq_gemm(x, w.qweight, w.scales, w.zeros, w.bias, w.group_size, w.bits)
+
+
+def make_weight(n, k, bits_, group, symmetric, seed, with_bias=True):
+    from dexter_labs_b200.quant import quantize
+
+    gen = torch.Generator().manual_seed(seed)
+    w = (torch.randn(n, k, generator=gen) * 0.02).to(torch.bfloat16)
+    b = torch.randn(n, generator=gen).to(torch.bfloat16) if with_bias else None
+    return quantize(w, bits=bits_, group_size=group, bias=b, symmetric=symmetric)
+
+
+def test_group_bounds_cover_everything(b200_lib):
+    from dexter_labs_b200.tp import group_bounds
+
+    for groups in (1, 3, 24, 40, 108, 112):
+        for world in (1, 2, 4, 8):
+            spans = [group_bounds(groups, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == groups
+            for a, b in zip(spans, spans[1:]):
+                assert a[1] == b[0]
+            sizes = [b - a for a, b in spans]
+            assert max(sizes) - min(sizes) <= 1
+
+
+@pytest.mark.parametrize("nbits,group,sym", [(4, 128, True), (4, 64, False), (8, 128, False), (8, 768, True)])
+@pytest.mark.parametrize("world", [2, 4, 3])
+def test_shards_are_slices_of_the_dense_weight(nbits, group, sym, world, b200_lib, oracle):
+    from dexter_labs_b200.tp import split_columns, split_rows
+
+    k, n = 768, 96
+    full = make_weight(n, k, nbits, group, sym, seed=world)
+    dense = oracle.c_dequantize(full.qweight.numpy(), bits(full.scales),
+                                None if full.zeros is None else bits(full.zeros), group, nbits)
+    seen_rows = 0
+    for rank in range(world):
+        if n % world == 0:
+            col = split_columns(full, rank, world)
+            d = oracle.c_dequantize(col.qweight.numpy(), bits(col.scales),
+                                    None if col.zeros is None else bits(col.zeros), group, nbits)
+            n0, n1 = rank * n // world, (rank + 1) * n // world
+            assert np.array_equal(d, dense[:, n0:n1])  # bit-identical to slicing the weight
+            assert torch.equal(col.bias, full.bias[n0:n1])
+        else:
+            with pytest.raises(ValueError):
+                split_columns(full, rank, world)
+        if (k // group) < world:
+            with pytest.raises(ValueError):
+                split_rows(full, rank, world)
+            continue
+        row, (k0, k1) = split_rows(full, rank, world)
+        assert k0 == seen_rows and (k1 - k0) % group == 0
+        seen_rows = k1
+        d = oracle.c_dequantize(row.qweight.numpy(), bits(row.scales),
+                                None if row.zeros is None else bits(row.zeros), group, nbits)
+        assert np.array_equal(d, dense[k0:k1])
+        assert (row.bias is not None) == (rank == 0)
+    if (k // group) >= world:
+        assert seen_rows == k
+
+
+def test_row_parallel_sum_matches_unsharded(b200_lib, oracle):
+    from dexter_labs_b200.tp import split_rows
+
+    torch.manual_seed(3)
+    k, n, m, world = 1024, 64, 5, 4
+    full = make_weight(n, k, 4, 128, True, seed=11)
+    x = torch.randn(m, k).to(torch.bfloat16)
+    want = oracle_gemm(x, full).float()
+    acc = torch.zeros(m, n)
+    for rank in range(world):
+        shard, (k0, k1) = split_rows(full, rank, world)
+        acc += oracle_gemm(x[:, k0:k1].contiguous(), shard).float()
+    err = (acc - want).abs().max().item() / max(want.abs().max().item(), 1e-6)
+    assert err < 1e-2, err
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _tp_worker(rank, world, port, collective, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from dexter_labs_b200 import tp
+
+        tp.PRESETS["tiny"] = (256, 512, 2)
+        ls = tp.LayerSet.build("tiny", rank=rank, world=world, bits=4, group_size=128, device="cpu",
+                               seed=5, collective=collective, gemm=oracle_gemm)
+        torch.manual_seed(0)
+        x = torch.randn(7, 256).to(torch.bfloat16)
+        ctx = torch.randn(7, 256).to(torch.bfloat16)
+        y = ls.forward(x, ctx)
+        results[rank] = y.float().numpy()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("collective", ["rs_ag", "all_reduce"])
+def test_two_rank_layer_set_matches_single_rank(collective, b200_lib, oracle):
+    from dexter_labs_b200 import tp
+
+    tp.PRESETS["tiny"] = (256, 512, 2)
+    single = tp.LayerSet.build("tiny", bits=4, group_size=128, device="cpu", seed=5, gemm=oracle_gemm)
+    assert single.num_gemms == 20
+    torch.manual_seed(0)
+    x = torch.randn(7, 256).to(torch.bfloat16)
+    ctx = torch.randn(7, 256).to(torch.bfloat16)
+    want = single.forward(x, ctx).float().numpy()
+
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_tp_worker, args=(world, _free_port(), collective, results), nprocs=world, join=True)
+    for rank in range(world):
+        got = results[rank]
+        err = np.abs(got - want).max() / max(np.abs(want).max(), 1e-6)
+        # partial sums are rounded to bf16 before the cross-rank sum: 1e-2 per the stated tolerance
+        assert err < 1e-2, (rank, err)
+    assert np.array_equal(results[0], results[1])  # every rank ends with the same replicated x
+
+
+def test_layer_set_accounting(b200_lib):
+    from dexter_labs_b200 import tp
+
+    tp.PRESETS["tiny"] = (256, 512, 2)
+    ls = tp.LayerSet.build("tiny", bits=4, group_size=128, device="cpu", seed=1, bias=False,
+                           gemm=oracle_gemm)
+    per_block = 8 * (256 * 256 // 2 + 2 * 256 * 2) + 2 * (256 * 512 // 2) + (2 * 512 + 4 * 256) * 2
+    assert ls.weight_bytes == 2 * per_block
+    assert ls.flops(7) == 2 * (8 * 2 * 7 * 256 * 256 + 2 * 2 * 7 * 256 * 512)
