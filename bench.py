@@ -1,0 +1,376 @@
+#!/usr/bin/env python3
+"""Benchmark of the B200 weight-only quantised GEMM backend.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (all N): the linear-layer set of the 5B backbone -- 30 blocks x 10 int4
+(group 128, symmetric, bias) linears at M = 83 tokens, 300 GEMMs and 2.53 GB of
+packed weights per pass, which contains the headline shape M=83, K=3072, N=14336
+(FFN-up) 30 times.  One "step" is one pass over the set.  With N > 1 the set is
+tensor-parallel (column shards for q/k/v/up, row shards for o/down, one
+reduce-scatter + all-gather after each row-parallel linear), so scaling is strong.
+The headline single GEMM is timed as well (16 rotating weight buffers, 363 MB, so
+L2 cannot hold them) and reported under "gemm".
+
+Prints ONE JSON line on rank 0.  `--impl reference` times the reference's algorithm
+(its torch dequantise-then-matmul op sequence, restated in oracle/) on the host
+cores for the same metric; it is the one place besides the cpu_baseline leg where
+this file touches oracle/.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M_TOKENS = 83
+PRESET = "5b"
+METRIC = "w4a16_5b_layer_set_ms"
+# DRAM bytes / algorithmic bytes of one wq_gemm_tc launch, from the ncu capture summarised in
+# profiles/wq_gemm_tc_w4_m83_k3072_n14336.md (23.27 MB read for 22.71 MB of packed weights + scales)
+DRAM_OVER_ALGORITHMIC = 1.025
+
+
+def load_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        p = json.loads(path.read_text())
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops"],
+                "tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.lines = []
+        self.proc = None
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, maxes, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                maxes.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None,
+                "sm_max_mhz": max(maxes) if maxes else None, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+# --------------------------------------------------------------- reference arm
+def cpu_block_ms(blocks_timed: int, reps: int):
+    """Reference algorithm on the host cores: `blocks_timed` blocks of the set, median ms."""
+    import torch
+
+    from dexter_labs_b200 import tp
+    from oracle import wq_oracle
+
+    def cpu_gemm(x, w):
+        return wq_oracle.torch_wq_gemm(x, w.qweight, w.scales, w.zeros, w.bias, w.group_size, w.bits)
+
+    ls = tp.LayerSet.build(PRESET, blocks=blocks_timed, device="cpu", seed=0, gemm=cpu_gemm)
+    torch.manual_seed(0)
+    x = torch.randn(M_TOKENS, ls.dim).to(torch.bfloat16)
+    ctx = torch.randn(M_TOKENS, ls.dim).to(torch.bfloat16)
+    ls.forward(x, ctx)  # warm-up
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        ls.forward(x, ctx)
+        times.append((time.perf_counter() - t0) * 1e3)
+    return statistics.median(times) / blocks_timed, torch.get_num_threads()
+
+
+def run_reference(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from dexter_labs_b200 import tp
+
+    blocks = tp.PRESETS[PRESET][2]
+    # each step: one block's ten GEMMs (a bounded sample), scaled to the 30 blocks of a pass
+    for _ in range(max(args.warmup, 1) - 1):
+        cpu_block_ms(1, 1)
+    per_block_ms, threads = cpu_block_ms(1, max(args.steps, 1))
+    value = per_block_ms * blocks
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "ms", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": value, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "ms", "cores": threads, "kind": "port",
+                         "sample": "one block (10 of 300 GEMMs) per step, x30; torch CPU op "
+                                   "sequence of the reference (dequantise whole weight, matmul, bias)"},
+        "e2e": {"value": value, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {"workload": "5B backbone linear set: 30 blocks x (self q,k,v,o; cross q,k,v,o; ffn up,down), "
+                        "int4 group 128 symmetric + bias, M=83, seeded random weights",
+            "gemms_per_step": 300, "tokens": M_TOKENS, "dim": 3072, "ffn_dim": 14336,
+            "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single",
+            "collectives": "reduce_scatter+all_gather after each row-parallel linear" if n_gpus > 1 else "none",
+            "l2": "2.53 GB of weights per pass stream through the 126 MB L2; single-GEMM figure rotates "
+                  "16 weight buffers (363 MB)"}
+
+
+# --------------------------------------------------------------------- our arm
+def time_graph(graph, iters: int):
+    import torch
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1)
+
+
+def single_gemm_figures(d, ops, peaks) -> dict:
+    """The headline GEMM alone: M=83, K=3072, N=14336, int4 g128, 16 rotating weights."""
+    import torch
+
+    m, k, n = M_TOKENS, 3072, 14336
+    torch.manual_seed(0)
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    base = d.quantize((torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16), bits=4,
+                      group_size=128, symmetric=True)
+    weights = [(torch.randint(0, 256, base.qweight.shape, dtype=torch.uint8, device="cuda"),
+                base.scales.clone()) for _ in range(16)]
+
+    def body():
+        for q, s in weights:
+            ops.w4a16(x, q, s, None, None, 128)
+
+    body()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        body()
+    graph.replay()
+    torch.cuda.synchronize()
+    best = min(time_graph(graph, 4) for _ in range(7)) * 1e3 / (4 * len(weights))  # us per GEMM
+    wbytes = base.nbytes
+    flops = 2.0 * m * k * n
+    t_mem = wbytes / (peaks["hbm_gbs"] * 1e3)      # us
+    t_mma = flops / (peaks["tflops"] * 1e6)        # us
+    return {"shape": [m, k, n], "us": best, "tflops": flops / best * 1e-6, "gbs": wbytes / best * 1e-3,
+            "frac_hbm": t_mem / best, "frac_tensor": t_mma / best, "frac_roofline": max(t_mem, t_mma) / best,
+            "roofline_us": max(t_mem, t_mma), "launches_timed": 7 * 4 * len(weights)}
+
+
+def run_ours(args) -> int:
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print(f"bench.py --gpus {args.gpus} must be launched with torch.distributed.run "
+                  f"--nproc-per-node {args.gpus}", file=sys.stderr)
+            return 2
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    import dexter_labs_b200 as d  # loads the CUDA library; fails loudly if it is missing
+    from dexter_labs_b200 import ops, tp
+
+    peaks = load_peaks()
+    ls = tp.LayerSet.build(PRESET, rank=rank, world=world, bits=4, group_size=128, symmetric=True,
+                           bias=True, device=f"cuda:{local}", seed=0)
+    torch.manual_seed(0)
+    host_x = torch.randn(M_TOKENS, ls.dim).to(torch.bfloat16).pin_memory()
+    host_ctx = torch.randn(M_TOKENS, ls.dim).to(torch.bfloat16).pin_memory()
+    host_y = torch.empty(M_TOKENS, ls.dim, dtype=torch.bfloat16).pin_memory()
+    x = host_x.cuda()
+    ctx = host_ctx.cuda()
+
+    # one pass, eagerly, then captured into a CUDA graph (kernels + collectives)
+    y = ls.forward(x, ctx)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    use_graph = True
+    try:
+        with torch.cuda.graph(graph):
+            y = ls.forward(x, ctx)
+    except Exception as exc:  # noqa: BLE001 - e.g. a collective that cannot be captured
+        use_graph = False
+        if rank == 0:
+            print(f"graph capture failed ({exc}); timing eager launches", file=sys.stderr)
+
+    def step():
+        if use_graph:
+            graph.replay()
+        else:
+            ls.forward(x, ctx)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    elapsed = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    ms_per_step = elapsed.item() / args.steps
+
+    # end to end through the public API with host buffers: H2D of x and ctx, the pass, D2H of y
+    def e2e_step():
+        x.copy_(host_x, non_blocking=True)
+        ctx.copy_(host_ctx, non_blocking=True)
+        step()
+        host_y.copy_(y, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    e2e = torch.tensor([f0.elapsed_time(f1)], device="cuda")
+    if world > 1:
+        dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
+    e2e_ms = e2e.item() / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    total_bytes = torch.tensor([float(ls.weight_bytes)], device="cuda")
+    if world > 1:
+        dist.all_reduce(total_bytes)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    status = ops.last_status()
+    set_flops = 2.0 * M_TOKENS * (8 * 3072 * 3072 + 2 * 3072 * 14336) * ls.blocks
+    set_bytes = total_bytes.item()
+    launches_per_step = ls.num_gemms
+    t_mem_ms = set_bytes / world / (peaks["hbm_gbs"] * 1e6)
+    t_mma_ms = set_flops / world / (peaks["tflops"] * 1e9)
+    roofline_ms = max(t_mem_ms, t_mma_ms)
+    # dominant kernel: wq_gemm_tc<4,false>; per-launch averages over the pass (per rank)
+    us_per_launch = ms_per_step * 1e3 / launches_per_step
+    flops_per_launch = set_flops / world / launches_per_step
+    bytes_per_launch = set_bytes / world / launches_per_step
+    bound = "tensor" if t_mma_ms >= t_mem_ms else "hbm"
+    if bound == "tensor":
+        achieved, peak, unit = flops_per_launch / us_per_launch * 1e-6, peaks["tflops"], "TFLOP/s"
+    else:
+        achieved, peak, unit = bytes_per_launch / us_per_launch * 1e-3, peaks["hbm_gbs"], "GB/s"
+
+    line = {
+        "metric": METRIC, "value": ms_per_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+        "clocks": clocks,
+        "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": 2 * host_x.numel() * 2,
+                "d2h_bytes_per_step": host_y.numel() * 2},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+                     "frac": achieved / peak, "traffic": bytes_per_launch * DRAM_OVER_ALGORITHMIC,
+                     "kernel": "wq_gemm_tc<4,false>", "peak_source": f"{peaks['source']} (burst)",
+                     "algorithmic_bytes_per_launch": bytes_per_launch,
+                     "algorithmic_flops_per_launch": flops_per_launch,
+                     "us_per_launch": us_per_launch,
+                     "frac_hbm": (bytes_per_launch / us_per_launch * 1e-3) / peaks["hbm_gbs"]},
+        "layer_set": {"weight_bytes": set_bytes, "flops": set_flops, "roofline_ms": roofline_ms,
+                      "frac_roofline": roofline_ms / ms_per_step, "graph": use_graph,
+                      "kernel_status": status},
+    }
+    if world == 1:
+        line["gemm"] = single_gemm_figures(d, ops, peaks)
+        per_block_ms, threads = cpu_block_ms(1, 3)
+        line["cpu_baseline"] = {"value": per_block_ms * ls.blocks, "unit": "ms", "cores": threads,
+                                "kind": "port",
+                                "sample": "one block (10 of 300 GEMMs), median of 3, x30; torch CPU op "
+                                          "sequence of the reference on the host cores"}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0 if status == 0 else 1
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    args = ap.parse_args()
+    return run_reference(args) if args.impl == "reference" else run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
