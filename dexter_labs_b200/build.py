@@ -1,6 +1,7 @@
 """In-tree build of the CUDA library (``libdexter_b200.so``) for sm_100a.
 
-``python -m dexter_labs_b200.build`` (or :func:`build`) runs nvcc on
+``python dexter_labs_b200/build.py`` (run as a script, so the package -- which loads the
+library on import -- is not imported first) or :func:`build` runs nvcc on
 ``csrc/wq_gemm.cu`` and leaves the shared library next to this file, where
 :mod:`dexter_labs_b200._lib` loads it.  nvcc cross-compiles without a GPU.
 """

@@ -77,8 +77,12 @@ def oracle():
 @pytest.fixture(scope="session")
 def b200_lib():
     """Build (if stale) and load the CUDA library; needs nvcc but no GPU."""
-    from dexter_labs_b200 import build as b
+    import importlib.util
 
+    # by path: importing the package would load the (possibly stale) library first
+    spec = importlib.util.spec_from_file_location("_dxb_build", ROOT / "dexter_labs_b200" / "build.py")
+    b = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(b)
     b.build()
     from dexter_labs_b200 import _lib
 
