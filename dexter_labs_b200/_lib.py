@@ -15,7 +15,7 @@ OK = 0
 ERRORS = {
     -1: "DXB_ERR_BITS", -2: "DXB_ERR_NULL", -3: "DXB_ERR_SHAPE", -4: "DXB_ERR_UNSUPPORTED",
     -5: "DXB_ERR_WORKSPACE", -6: "DXB_ERR_TENSORMAP", -7: "DXB_ERR_CUDA",
-    -8: "DXB_ERR_KERNEL_TIMEOUT",
+    -8: "DXB_ERR_KERNEL_TIMEOUT", -9: "DXB_ERR_SCRATCH_LIMIT",
 }
 
 # name -> (restype, argtypes); one entry per symbol declared in include/dexter_b200.h
@@ -23,6 +23,8 @@ SIGNATURES = {
     "dxb_wq_gemm": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
                             c_int, c_void_p]),
+    "dxb_wq_gemm_static": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "dxb_w4a16": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_int64, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "dxb_w8a16": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -45,7 +47,7 @@ def load() -> ctypes.CDLL:
         return _lib
     if not LIB_PATH.exists():
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m dexter_labs_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python dexter_labs_b200/build.py` "
             "(needs nvcc; there is no non-CUDA fallback)")
     lib = ctypes.CDLL(str(LIB_PATH))
     for name, (restype, argtypes) in SIGNATURES.items():

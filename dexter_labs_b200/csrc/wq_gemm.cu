@@ -979,6 +979,57 @@ int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const
   return DXB_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Scratch that lives inside the library image, for callers that must not
+// allocate device memory (see dxb_wq_gemm_static in the header).  Zero at load
+// time; every GPU that loads the library keeps these 24 MiB until the process
+// exits.  In host code the symbol below is only a stand-in: its device address
+// has to be asked for with cudaGetSymbolAddress, per device.
+constexpr size_t kStaticScratchBytes = static_cast<size_t>(24) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace dx {
+constexpr int kMaxDevices = 64;
+// Device address of g_static_scratch on the CURRENT device, looked up once per device.
+static int static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* addr[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return DXB_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();  // clear the sticky-less error so later calls start clean
+      return DXB_ERR_CUDA;
+    }
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return DXB_OK;
+}
+}  // namespace dx
+
+int dxb_wq_gemm_static(int bits, const void* x, int64_t ldx, const void* qweight,
+                       const void* scales, const void* zeros, const void* bias, void* out,
+                       int64_t ldo, int M, int N, int K, int group_size, void* cuda_stream) {
+  using namespace dx;
+  int rc = check_args(bits, x, ldx, qweight, scales, out, ldo, M, N, K, group_size);
+  if (rc != DXB_OK) return rc;
+  if (M == 0) return DXB_OK;
+  if (dxb_workspace_bytes(M, N, K, bits) > kStaticScratchBytes) return DXB_ERR_SCRATCH_LIMIT;
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc != DXB_OK) return rc;
+  // The array keeps whatever the previous call left.  Partial sums are always written
+  // before they are read, but the status word and the tile counters must start at zero.
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (cudaMemsetAsync(scratch, 0, kStatusBytes + counters_bytes(0), stream) != cudaSuccess)
+    return DXB_ERR_CUDA;
+  return dxb_wq_gemm(bits, x, ldx, qweight, scales, zeros, bias, out, ldo, M, N, K, group_size,
+                     scratch, kStaticScratchBytes, 0, cuda_stream);
+}
+
 int dxb_w4a16(const void* x, int64_t ldx, const void* qweight, const void* scales,
               const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
               int group_size, void* workspace, size_t workspace_bytes, void* cuda_stream) {
@@ -1053,6 +1104,9 @@ const char* dxb_strerror(int code) {
     case DXB_ERR_TENSORMAP: return "could not encode a TMA tensor map";
     case DXB_ERR_CUDA: return "CUDA launch or runtime error";
     case DXB_ERR_KERNEL_TIMEOUT: return "a bounded wait inside the kernel ran out";
+    case DXB_ERR_SCRATCH_LIMIT:
+      return "problem needs more scratch than the 24 MiB built into the library "
+             "(use dxb_wq_gemm with a caller-provided workspace)";
     default: return "unknown error";
   }
 }

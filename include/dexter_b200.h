@@ -41,7 +41,8 @@ enum {
   DXB_ERR_WORKSPACE = -5,      /* workspace NULL or smaller than dxb_workspace_bytes() */
   DXB_ERR_TENSORMAP = -6,      /* cuTensorMapEncodeTiled refused the tensor */
   DXB_ERR_CUDA = -7,           /* launch failed; see cudaGetLastError */
-  DXB_ERR_KERNEL_TIMEOUT = -8  /* a bounded in-kernel wait ran out (read via dxb_read_status) */
+  DXB_ERR_KERNEL_TIMEOUT = -8, /* a bounded in-kernel wait ran out (read via dxb_read_status) */
+  DXB_ERR_SCRATCH_LIMIT = -9   /* dxb_wq_gemm_static: needs more than the built-in 24 MiB */
 };
 
 /*
@@ -67,6 +68,33 @@ int dxb_w4a16(const void* x, int64_t ldx, const void* qweight, const void* scale
 int dxb_w8a16(const void* x, int64_t ldx, const void* qweight, const void* scales,
               const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
               int group_size, void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/*
+ * Same GEMM as dxb_wq_gemm for callers that cannot hand over a workspace because
+ * they are not allowed to allocate device memory at all: code running inside
+ * another framework's memory plan (a serving runtime that has already carved up
+ * the whole GPU, a plugin whose host forbids cudaMalloc on its threads), or code
+ * that must stay free of allocator calls because those may synchronise or fail
+ * at a bad moment.  This entry point has no counterpart in the reference; it is
+ * an addition of this library.
+ *
+ * The split-K scratch (status word, tile counters, fp32 partial sums) is a fixed
+ * 24 MiB array inside the library image; each GPU that loads the library holds it
+ * until the process exits.  The call itself calls no cudaMalloc / cudaFree and no
+ * allocating library routine.  Limits and rules:
+ *   - a problem whose scratch need (dxb_workspace_bytes) exceeds 24 MiB is refused
+ *     with DXB_ERR_SCRATCH_LIMIT and nothing is launched (the shapes of the 5B and
+ *     14B backbones at up to 128 tokens per launch fit);
+ *   - the first call on each device looks up the array's device address; make that
+ *     first call outside any stream capture;
+ *   - all calls share the one array: the counters and the status word are cleared
+ *     (cudaMemsetAsync on `cuda_stream`) at the start of every call, partial sums
+ *     are overwritten before use; two calls that may run on the GPU at the same
+ *     time (different streams, no ordering) race on it and must not be made.
+ */
+int dxb_wq_gemm_static(int bits, const void* x, int64_t ldx, const void* qweight,
+                       const void* scales, const void* zeros, const void* bias, void* out,
+                       int64_t ldo, int M, int N, int K, int group_size, void* cuda_stream);
 
 /* Bytes of workspace dxb_wq_gemm needs for this problem on the current device. */
 size_t dxb_workspace_bytes(int M, int N, int K, int bits);
