@@ -84,6 +84,7 @@ struct WqParams {
   int max_slots;       // partial slots reserved per tile
   int nacc;            // accumulator buffers in TMEM (2 when NU <= 128)
   int group_shift;     // log2(group / 64) when that is a power of two, else -1
+  int cluster;         // CTAs per tile (thread-block cluster along x); 1 = no cluster
   long long* trace;    // only used when built with -DDXB_TRACE
 };
 
@@ -211,11 +212,19 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const uint32_t tmem0 = tmem_base_s;
 
   // This CTA's contiguous range of (tile, unit) work.
+  // Cluster mode: the `cluster` CTAs of one cluster share one tile, each taking a
+  // contiguous slice of its K units; they add their partial sums through distributed
+  // shared memory at the end (no global scratch, no counters).
   const int TU = p.total_units;
   const int G = static_cast<int>(gridDim.x);
-  const int u_begin = static_cast<int>(range_begin(blockIdx.x, TU, G));
-  const int u_end = static_cast<int>(range_begin(blockIdx.x + 1, TU, G));
   const int U = p.units_per_tile;
+  const int C = p.cluster;
+  const int crank = C > 1 ? static_cast<int>(blockIdx.x % C) : 0;
+  const int ctile = C > 1 ? static_cast<int>(blockIdx.x / C) : 0;
+  const int u_begin = C > 1 ? ctile * U + crank * U / C
+                            : static_cast<int>(range_begin(blockIdx.x, TU, G));
+  const int u_end = C > 1 ? ctile * U + (crank + 1) * U / C
+                          : static_cast<int>(range_begin(blockIdx.x + 1, TU, G));
   const int tile_begin = u_begin / U;
   const int ku_begin = u_begin - tile_begin * U;
   volatile int* abortp = &abort_flag;
@@ -397,6 +406,27 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
               }
               *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.ldo + n) = pk;
             }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
+      } else if (C > 1) {
+        // Cluster mode: park the fp32 sums in this CTA's shared memory (the pipeline
+        // rings are idle by now: every load has been consumed) for the cluster reduce.
+        for (int c0 = 0; c0 < p.NU; c0 += 16) {
+          uint32_t ra[8], rb[8];
+          tmem_ld_16x128b_x4(d_tmem + c0, ra);
+          tmem_ld_16x128b_x4(d_tmem + (16u << 16) + c0, rb);
+          tc_wait_ld();
+#pragma unroll
+          for (int rep = 0; rep < 4; ++rep) {
+            const int m = c0 + 4 * rep + c;
+            if (m < p.M)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
+                               smem0 + static_cast<uint32_t>(m * kTileN + n_local) * 4u),
+                           "r"(ra[2 * rep]), "r"(ra[2 * rep + 1]), "r"(rb[2 * rep]),
+                           "r"(rb[2 * rep + 1])
+                           : "memory");
           }
         }
         tc_fence_before();
@@ -635,6 +665,41 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   tc_fence_before();
   __syncthreads();
+  if (C > 1) {
+    // Every CTA of the cluster has its partial tile in shared memory: CTA `crank` sums
+    // its share of the token rows over the cluster in rank order (deterministic), adds
+    // the bias and writes bf16.  The second barrier keeps peers' memory alive until read.
+    cluster_sync_all();
+    const int rows_per = (p.M + C - 1) / C;
+    const int m_lo = crank * rows_per;
+    const int m_hi = (m_lo + rows_per) < p.M ? (m_lo + rows_per) : p.M;
+    const bool has_bias = p.bias != nullptr;
+    for (int i = threadIdx.x; i < (m_hi - m_lo) * 32; i += kThreads) {
+      const int m = m_lo + (i >> 5);
+      const int c4 = (i & 31) * 4;
+      const int n = ctile * kTileN + c4;
+      if (n < p.N) {
+        const uint32_t local = smem0 + static_cast<uint32_t>(m * kTileN + c4) * 4u;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < C; ++r) {
+          const float4 v = ld_dsmem_f4(dsmem_addr(local, r));
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        uint2 pk;
+        if (has_bias) {
+          const uint2 bb = *reinterpret_cast<const uint2*>(p.bias + n);
+          const uint32_t r01 = cvt_bf16x2(acc.y, acc.x), r23 = cvt_bf16x2(acc.w, acc.z);
+          pk.x = cvt_bf16x2(bf16hi_f32(r01) + bf16hi_f32(bb.x), bf16lo_f32(r01) + bf16lo_f32(bb.x));
+          pk.y = cvt_bf16x2(bf16hi_f32(r23) + bf16hi_f32(bb.y), bf16lo_f32(r23) + bf16lo_f32(bb.y));
+        } else {
+          pk.x = cvt_bf16x2(acc.y, acc.x);
+          pk.y = cvt_bf16x2(acc.w, acc.z);
+        }
+        *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.ldo + n) = pk;
+      }
+    }
+    cluster_sync_all();
+  }
   if (threadIdx.x == 0) DX_TRACE(7, 0);
   if (warp == 1) tmem_dealloc(tmem0, 512);
   if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, DXB_ERR_KERNEL_TIMEOUT);
@@ -801,8 +866,12 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   pl.w_stages = w_stages;
   pl.smem_bytes = static_cast<size_t>(pl.w_stages) * kWStage +
                   static_cast<size_t>(pl.stages) * pl.x_stage_bytes + 1024;
-  int ctas = sms;
-  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  // Grid: with an explicit cap, that many CTAs stream-K over all units.  By default one
+  // CTA per tile when the tiles fit the SMs (splitting them through global scratch costs
+  // more than it gains; the launcher splits tiles across a thread-block cluster instead,
+  // where it can), else one CTA per SM, stream-K.
+  int ctas = pl.tiles <= sms ? pl.tiles : sms;
+  if (max_ctas > 0) ctas = max_ctas < sms ? max_ctas : sms;
   if (ctas > pl.total_units) ctas = pl.total_units;
   pl.ctas = ctas;
   pl.nacc = 2;
@@ -889,17 +958,74 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   p.trace = g_trace;
 
   auto kernel = wq_gemm_tc<BITS, HAS_ZERO>;
-  static thread_local int attr_dev[4] = {-1, -1, -1, -1};
+  static thread_local int attr_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
-  const int slot = (BITS == 8 ? 2 : 0) + (HAS_ZERO ? 1 : 0);
-  if (attr_dev[slot] != dev) {
+  if (attr_dev != dev) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemBudget + 1024) != cudaSuccess)
       return DXB_ERR_CUDA;
-    attr_dev[slot] = dev;
+    attr_dev = dev;
   }
-  kernel<<<pl.ctas, kThreads, pl.smem_bytes, stream>>>(tq, tx, p);
+
+  // Few tiles: split each tile's K range over a thread-block cluster (<= 8 CTAs) that
+  // reduces through distributed shared memory.  The cluster size is the largest one for
+  // which all clusters are resident at once; the answer is cached per configuration.
+  int cluster = 1;
+  if (max_ctas <= 0 && pl.tiles * 2 <= di.sms && pl.units_per_tile >= 2) {
+    static thread_local std::unordered_map<long long, int> cache;
+    const long long key = (static_cast<long long>(dev) << 48) ^ (static_cast<long long>(pl.tiles) << 28) ^
+                          (static_cast<long long>(pl.units_per_tile) << 8) ^ static_cast<long long>(pl.NU >> 4);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      cluster = it->second;
+    } else {
+      int cmax = di.sms / pl.tiles;
+      if (cmax > 8) cmax = 8;
+      if (cmax > pl.units_per_tile) cmax = pl.units_per_tile;
+      for (int c = cmax; c >= 2; --c) {
+        cudaLaunchConfig_t qcfg = {};
+        qcfg.gridDim = dim3(pl.tiles * c);
+        qcfg.blockDim = dim3(kThreads);
+        qcfg.dynamicSmemBytes = pl.smem_bytes;
+        cudaLaunchAttribute qattr[1];
+        qattr[0].id = cudaLaunchAttributeClusterDimension;
+        qattr[0].val.clusterDim.x = c;
+        qattr[0].val.clusterDim.y = 1;
+        qattr[0].val.clusterDim.z = 1;
+        qcfg.attrs = qattr;
+        qcfg.numAttrs = 1;
+        int resident = 0;
+        if (cudaOccupancyMaxActiveClusters(&resident, kernel, &qcfg) == cudaSuccess &&
+            resident >= pl.tiles) {
+          cluster = c;
+          break;
+        }
+        cudaGetLastError();
+      }
+      cache[key] = cluster;
+    }
+  }
+  p.cluster = cluster;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(cluster > 1 ? pl.tiles * cluster : pl.ctas);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = pl.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (cluster > 1) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  if (cudaLaunchKernelEx(&cfg, kernel, tq, tx, p) != cudaSuccess) {
+    cudaGetLastError();
+    return DXB_ERR_CUDA;
+  }
   return cudaGetLastError() == cudaSuccess ? DXB_OK : DXB_ERR_CUDA;
 }
 
