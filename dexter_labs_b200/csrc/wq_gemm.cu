@@ -307,24 +307,19 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       uint32_t a_tmem = tmem0 + kACol0;
       bool ok = true;
       int u = u_begin, ku0 = ku_begin, done = 0;
+      const bool leader = elect_one();  // the one lane that issues; fixed for the whole loop
       while (u < u_end && ok) {
         const int left = u_end - u;
         const int nun = left < (U - ku0) ? left : (U - ku0);
         ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarAccEmpty + b), accph ^ 1u, abortp));
         if (!ok) break;
         const uint32_t d_tmem = tmem0 + b * p.NU;
+        uint32_t accumulate = 0;
         for (int i = 0; i < nun; ++i) {
-          if (lane == 0) DX_TRACE(0, done);
-          ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarReady + t), ph, abortp));
-          if (!ok) break;
-          if (lane == 0) DX_TRACE(1, done);
+          if (!mbar_wait(bar0 + 8 * (kBarReady + t), ph, abortp)) { ok = false; break; }
           tc_fence_after();
-          if (elect_one()) {
-            if (i == 0) {
-              mma_ts(d_tmem, a_tmem, xd, idesc, 0u);
-            } else {
-              mma_ts(d_tmem, a_tmem, xd, idesc, 1u);
-            }
+          if (leader) {
+            mma_ts(d_tmem, a_tmem, xd, idesc, accumulate);
 #pragma unroll
             for (int kk = 1; kk < 4; ++kk) mma_ts(d_tmem, a_tmem + kk * 8, xd + kk * 2, idesc, 1u);
             if (PLANES == 2) {
@@ -332,19 +327,18 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
               for (int kk = 0; kk < 4; ++kk)
                 mma_ts(d_tmem, a_tmem + 32 + kk * 8, xd + plane16 + kk * 2, idesc, 1u);
             }
-            DX_TRACE(5, done);
             tc_commit(bar0 + 8 * (kBarFree + t));
           }
-          __syncwarp();
+          accumulate = 1;
           if (lane == 0) DX_TRACE(3, done);
           ++done;
           xd += x_stage16;
           a_tmem += A_STAGE_COLS;
           if (++t == kAStages) { t = 0; ph ^= 1u; xd = xdesc0; a_tmem = tmem0 + kACol0; }
         }
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (elect_one()) tc_commit(bar0 + 8 * (kBarAccFull + b));
-        __syncwarp();
+        if (leader) tc_commit(bar0 + 8 * (kBarAccFull + b));
         u += nun;
         ku0 = 0;
         if (++b == 2) { b = 0; accph ^= 1u; }
@@ -680,10 +674,14 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const int n = ctile * kTileN + c4;
       if (n < p.N) {
         const uint32_t local = smem0 + static_cast<uint32_t>(m * kTileN + c4) * 4u;
+        float4 v[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          v[r] = r < C ? ld_dsmem_f4(dsmem_addr(local, r)) : make_float4(0.f, 0.f, 0.f, 0.f);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < C; ++r) {
-          const float4 v = ld_dsmem_f4(dsmem_addr(local, r));
-          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {  // rank order: the sum does not depend on timing
+          acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w;
         }
         uint2 pk;
         if (has_bias) {
