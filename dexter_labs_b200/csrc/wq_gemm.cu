@@ -229,16 +229,19 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const int ku_begin = u_begin - tile_begin * U;
   volatile int* abortp = &abort_flag;
 
-  if (warp == 0) {
+  if (warp == 0 || warp == 3) {
     // ============================================ TMA producer: packed weights
+    // Two producer warps (0 and 3) take alternate units, which doubles the issue rate.
     // The whole warp runs the loop (so addresses and coordinates stay in uniform
     // registers, which the TMA instruction wants); one elected lane issues.
     {
-      int tile = tile_begin, ku = ku_begin, s = 0;
+      const int pi = warp == 0 ? 0 : 1;
+      int tile = tile_begin, ku = ku_begin + pi, s = pi;
+      while (ku >= U) { ku -= U; ++tile; }
       uint32_t ph = 0;
       int issued = 0;
       bool ok = true;
-      for (int u = u_begin; u < u_end; ++u) {
+      for (int u = u_begin + pi; u < u_end; u += 2) {
         ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarEmptyW + s), ph ^ 1u, abortp));
         if (!ok) break;
         if (elect_one()) {
@@ -248,15 +251,15 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
         __syncwarp();
         ++issued;
-        if (++s == SW) { s = 0; ph ^= 1u; }
-        if (++ku == U) { ku = 0; ++tile; }
+        s += 2;
+        if (s >= SW) { s -= SW; ph ^= 1u; }
+        ku += 2;
+        while (ku >= U) { ku -= U; ++tile; }
       }
       if (!ok && lane == 0) {
         // Leaving early: let the copies already issued land before the CTA exits.
-        for (int j = (issued > SW ? issued - SW : 0); j < issued; ++j)
-          for (int spin = 0; spin < 200000; ++spin)
-            if (mbar_try_wait(bar0 + 8 * (kBarFullW + j % SW), static_cast<uint32_t>(j / SW) & 1u))
-              break;
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {}
       }
     }
     __syncwarp();
