@@ -66,7 +66,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.gpu_index)],
+                 "-lms", "20", "-i", str(self.gpu_index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -305,6 +305,37 @@ def run_ours(args) -> int:
     e2e_ms = e2e.item() / args.steps
     clocks = sampler.stop() if rank == 0 else None
 
+    # Same linears with self q/k/v and cross k/v each issued as one N-concatenated launch
+    # (same arithmetic per column, but another K-split order, so equal only up to fp32
+    # summation order; 7 launches per block instead of 10); reported as an extra.
+    fused = tp.LayerSet(ls.dim, ls.ffn_dim, ls.blocks, rank, world, ls.bits, ls.group_size,
+                        ls.collective, True, [tp.LayerSet._fuse(r) for r in ls.layers])
+    yf = fused.forward(x, ctx)
+    torch.cuda.synchronize()
+    fused_ms = None
+    try:
+        fgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(fgraph):
+            yf = fused.forward(x, ctx)
+        for _ in range(3):
+            fgraph.replay()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(args.steps):
+            fgraph.replay()
+        g1.record()
+        barrier()
+        ft = torch.tensor([g0.elapsed_time(g1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ft, op=dist.ReduceOp.MAX)
+        fused_ms = ft.item() / args.steps
+        fused_same = float((yf.float() - y.float()).abs().max() / y.float().abs().max().clamp(min=1e-6))
+    except Exception as exc:  # noqa: BLE001
+        fused_same = None
+        if rank == 0:
+            print(f"fused-qkv variant not timed: {exc}", file=sys.stderr)
+
     total_bytes = torch.tensor([float(ls.weight_bytes)], device="cuda")
     if world > 1:
         dist.all_reduce(total_bytes)
@@ -345,6 +376,9 @@ def run_ours(args) -> int:
                      "algorithmic_flops_per_launch": flops_per_launch,
                      "us_per_launch": us_per_launch,
                      "frac_hbm": (bytes_per_launch / us_per_launch * 1e-3) / peaks["hbm_gbs"]},
+        "fused_qkv": {"ms_per_step": fused_ms, "launches_per_step": fused.num_gemms,
+                      "max_normalised_diff_vs_separate": fused_same,
+                      "frac_roofline": None if not fused_ms else roofline_ms / fused_ms},
         "layer_set": {"weight_bytes": set_bytes, "flops": set_flops, "roofline_ms": roofline_ms,
                       "frac_roofline": roofline_ms / ms_per_step, "graph": use_graph,
                       "kernel_status": status},
@@ -365,7 +399,7 @@ def run_ours(args) -> int:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     args = ap.parse_args()

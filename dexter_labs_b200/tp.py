@@ -30,7 +30,7 @@ import torch
 
 from .quant import QuantizedWeight, pack_nibbles, quantize
 
-__all__ = ["group_bounds", "split_columns", "split_rows", "ShardedLinear", "LayerSet", "PRESETS",
+__all__ = ["group_bounds", "split_columns", "split_rows", "concat_columns", "ShardedLinear", "LayerSet", "PRESETS",
            "unpack_nibbles"]
 
 # name -> (dim, ffn_dim, blocks); python/dexter/models/dreamzero/config.py:182-219
@@ -84,6 +84,28 @@ def split_rows(qw: QuantizedWeight, rank: int, world: int) -> Tuple[QuantizedWei
                             None if qw.zeros is None else qw.zeros[g0:g1].contiguous(),
                             qw.bias if rank == 0 else None, g, qw.bits, (k1 - k0, n))
     return shard, (k0, k1)
+
+
+def concat_columns(parts: List[QuantizedWeight]) -> QuantizedWeight:
+    """N-concatenation of packed weights that share K, group size and bit width.
+
+    Scales, zero points and bias are per column, so one GEMM on the concatenation does
+    the same arithmetic per column as separate GEMMs on the parts (bit-identical for a
+    fixed K-summation order; this is how separate q/k/v linears become one
+    ``dim -> 3*dim`` launch).
+    """
+    first = parts[0]
+    if any(p.shape[0] != first.shape[0] or p.bits != first.bits or p.group_size != first.group_size
+           or (p.zeros is None) != (first.zeros is None) or (p.bias is None) != (first.bias is None)
+           for p in parts):
+        raise ValueError("only weights with the same K, bits, group size and zero/bias presence concatenate")
+
+    def cat(ts):
+        return None if ts[0] is None else torch.cat(ts, dim=-1).contiguous()
+
+    return QuantizedWeight(cat([p.qweight for p in parts]), cat([p.scales for p in parts]),
+                           cat([p.zeros for p in parts]), cat([p.bias for p in parts]),
+                           first.group_size, first.bits, (first.shape[0], sum(p.shape[1] for p in parts)))
 
 
 @dataclass
@@ -141,6 +163,7 @@ class LayerSet:
     bits: int = 4
     group_size: int = 128
     collective: str = "rs_ag"  # "rs_ag" | "all_reduce"
+    fuse_qkv: bool = False     # one launch for self q,k,v and one for cross k,v (N-concatenation)
     layers: List[List[ShardedLinear]] = field(default_factory=list)
     gemm: GemmFn = _default_gemm
     process_group: Optional[object] = None
@@ -151,10 +174,10 @@ class LayerSet:
     def build(cls, preset: str, *, blocks: Optional[int] = None, rank: int = 0, world: int = 1,
               bits: int = 4, group_size: int = 128, symmetric: bool = True, bias: bool = True,
               device="cuda", seed: int = 0, collective: str = "rs_ag", gemm: GemmFn = _default_gemm,
-              process_group=None, weight_std: float = 0.02) -> "LayerSet":
+              process_group=None, weight_std: float = 0.02, fuse_qkv: bool = False) -> "LayerSet":
         dim, ffn, nblocks = PRESETS[preset]
         nblocks = blocks if blocks is not None else nblocks
-        self = cls(dim, ffn, nblocks, rank, world, bits, group_size, collective, [], gemm,
+        self = cls(dim, ffn, nblocks, rank, world, bits, group_size, collective, fuse_qkv, [], gemm,
                    process_group)
         for blk in range(nblocks):
             row: List[ShardedLinear] = []
@@ -168,8 +191,26 @@ class LayerSet:
                 full = quantize(w, bits=bits, group_size=g, bias=b, symmetric=symmetric)
                 row.append(self.shard(name, kind, full))
                 del w, full
+            if fuse_qkv:
+                row = self._fuse(row)
             self.layers.append(row)
         return self
+
+    @staticmethod
+    def _fuse(row: List[ShardedLinear]) -> List[ShardedLinear]:
+        """Replace (self q,k,v) and (cross k,v) by their per-rank N-concatenations."""
+        by = {l.name: l for l in row}
+        out: List[ShardedLinear] = []
+        for name in ("self_qkv", "self_o", "cross_q", "cross_kv", "cross_o", "ffn_up", "ffn_down"):
+            if name in by:
+                out.append(by[name])
+                continue
+            parts = [by[f"self_{c}"] for c in "qkv"] if name == "self_qkv" else [by["cross_k"], by["cross_v"]]
+            fused = concat_columns([p.weight for p in parts])
+            k = parts[0].full_shape[0]
+            out.append(ShardedLinear(name, "column", fused, (0, k),
+                                     (k, sum(p.full_shape[1] for p in parts))))
+        return out
 
     def shard(self, name: str, kind: str, full: QuantizedWeight) -> ShardedLinear:
         k, n = full.shape
@@ -183,7 +224,13 @@ class LayerSet:
     # ------------------------------------------------------------------ stats
     @property
     def num_gemms(self) -> int:
+        """Kernel launches per pass (7 per block when q/k/v are fused, else 10)."""
         return sum(len(r) for r in self.layers)
+
+    @property
+    def num_linears(self) -> int:
+        """Linears of the model computed per pass (10 per block either way)."""
+        return len(_BLOCK_PLAN) * self.blocks
 
     @property
     def weight_bytes(self) -> int:
@@ -224,14 +271,22 @@ class LayerSet:
         L = {l.name: l for l in self.layers[blk]}
         g = self.gemm
         # self attention: q, k, v column-parallel; the v shard stands in for the attention output
-        g(x, L["self_q"].weight)
-        g(x, L["self_k"].weight)
-        v = g(x, L["self_v"].weight)
+        if self.fuse_qkv:
+            qkv = g(x, L["self_qkv"].weight)
+            v = qkv[:, 2 * (qkv.shape[1] // 3):]
+        else:
+            g(x, L["self_q"].weight)
+            g(x, L["self_k"].weight)
+            v = g(x, L["self_v"].weight)
         x = self._reduce(g(self._row_input(v, L["self_o"]), L["self_o"].weight))
         # cross attention: q on x, k and v on the context
         g(x, L["cross_q"].weight)
-        g(ctx, L["cross_k"].weight)
-        cv = g(ctx, L["cross_v"].weight)
+        if self.fuse_qkv:
+            kv = g(ctx, L["cross_kv"].weight)
+            cv = kv[:, kv.shape[1] // 2:]
+        else:
+            g(ctx, L["cross_k"].weight)
+            cv = g(ctx, L["cross_v"].weight)
         x = self._reduce(g(self._row_input(cv, L["cross_o"]), L["cross_o"].weight))
         # FFN
         h = g(x, L["ffn_up"].weight)

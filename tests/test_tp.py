@@ -156,3 +156,23 @@ def test_layer_set_accounting(b200_lib):
     per_block = 8 * (256 * 256 // 2 + 2 * 256 * 2) + 2 * (256 * 512 // 2) + (2 * 512 + 4 * 256) * 2
     assert ls.weight_bytes == 2 * per_block
     assert ls.flops(7) == 2 * (8 * 2 * 7 * 256 * 256 + 2 * 2 * 7 * 256 * 512)
+
+
+def test_fused_qkv_is_bit_identical_to_separate_linears(b200_lib, oracle):
+    from dexter_labs_b200 import tp
+
+    tp.PRESETS["tiny"] = (256, 512, 2)
+    torch.manual_seed(0)
+    x = torch.randn(7, 256).to(torch.bfloat16)
+    ctx = torch.randn(7, 256).to(torch.bfloat16)
+    plain = tp.LayerSet.build("tiny", device="cpu", seed=5, gemm=oracle_gemm)
+    fused = tp.LayerSet.build("tiny", device="cpu", seed=5, gemm=oracle_gemm, fuse_qkv=True)
+    assert plain.num_gemms == 20 and fused.num_gemms == 14 and fused.num_linears == 20
+    assert plain.weight_bytes == fused.weight_bytes and plain.flops(7) == fused.flops(7)
+    assert torch.equal(plain.forward(x, ctx).view(torch.int16), fused.forward(x, ctx).view(torch.int16))
+    # the concatenation itself: one GEMM == three GEMMs, column block by column block
+    parts = [l.weight for l in plain.layers[0][:3]]
+    whole = oracle_gemm(x, tp.concat_columns(parts))
+    for i, part in enumerate(parts):
+        assert torch.equal(whole[:, 256 * i:256 * (i + 1)].contiguous().view(torch.int16),
+                           oracle_gemm(x, part).view(torch.int16))
