@@ -161,7 +161,8 @@ def workload_config(n_gpus: int) -> dict:
                         "int4 group 128 symmetric + bias, M=83, seeded random weights",
             "gemms_per_step": 300, "tokens": M_TOKENS, "dim": 3072, "ffn_dim": 14336,
             "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single",
-            "collectives": "reduce_scatter+all_gather after each row-parallel linear" if n_gpus > 1 else "none",
+            "collectives": "one NCCL all-reduce (or reduce-scatter + all-gather, --collective rs_ag) after each "
+                           "row-parallel linear" if n_gpus > 1 else "none",
             "l2": "2.53 GB of weights per pass stream through the 126 MB L2; single-GEMM figure rotates "
                   "16 weight buffers (363 MB)"}
 
@@ -212,6 +213,23 @@ def single_gemm_figures(d, ops, peaks) -> dict:
             "roofline_us": max(t_mem, t_mma), "launches_timed": 7 * 4 * len(weights)}
 
 
+def finish(world: int, code: int) -> None:
+    """Leave the process without tearing NCCL down.
+
+    The timed passes are CUDA graphs that contain NCCL kernels; destroying the
+    communicator while such graphs are alive can block for ever, so multi-rank runs
+    flush their output and exit directly once all work is synchronised.
+    """
+    import torch
+
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    if world > 1:
+        os._exit(code)
+    sys.exit(code)
+
+
 def run_ours(args) -> int:
     import torch
     import torch.distributed as dist
@@ -233,7 +251,7 @@ def run_ours(args) -> int:
 
     peaks = load_peaks()
     ls = tp.LayerSet.build(PRESET, rank=rank, world=world, bits=4, group_size=128, symmetric=True,
-                           bias=True, device=f"cuda:{local}", seed=0)
+                           bias=True, device=f"cuda:{local}", seed=0, collective=args.collective)
     torch.manual_seed(0)
     host_x = torch.randn(M_TOKENS, ls.dim).to(torch.bfloat16).pin_memory()
     host_ctx = torch.randn(M_TOKENS, ls.dim).to(torch.bfloat16).pin_memory()
@@ -340,9 +358,7 @@ def run_ours(args) -> int:
     if world > 1:
         dist.all_reduce(total_bytes)
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return 0
+        finish(world, 0)
 
     status = ops.last_status()
     set_flops = 2.0 * M_TOKENS * (8 * 3072 * 3072 + 2 * 3072 * 14336) * ls.blocks
@@ -391,9 +407,7 @@ def run_ours(args) -> int:
                                 "sample": "one block (10 of 300 GEMMs), median of 3, x30; torch CPU op "
                                           "sequence of the reference on the host cores"}
     print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
-    return 0 if status == 0 else 1
+    finish(world, 0 if status == 0 else 1)
 
 
 def main() -> int:
@@ -402,6 +416,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--collective", choices=("all_reduce", "rs_ag"), default="all_reduce",
+                    help="how row-parallel partial sums are combined when N > 1")
     args = ap.parse_args()
     return run_reference(args) if args.impl == "reference" else run_ours(args)
 
