@@ -159,7 +159,7 @@ def run_reference(args) -> int:
 def workload_config(n_gpus: int) -> dict:
     return {"workload": "5B backbone linear set: 30 blocks x (self q,k,v,o; cross q,k,v,o; ffn up,down), "
                         "int4 group 128 symmetric + bias, M=83, seeded random weights",
-            "gemms_per_step": 300, "tokens": M_TOKENS, "dim": 3072, "ffn_dim": 14336,
+            "gemms_per_step": 300, "schedule": "per block: self q,k,v and cross k,v on parallel streams, then o, cross q, cross o, up, down; one CUDA graph per pass", "tokens": M_TOKENS, "dim": 3072, "ffn_dim": 14336,
             "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single",
             "collectives": "one NCCL all-reduce (or reduce-scatter + all-gather, --collective rs_ag) after each "
                            "row-parallel linear" if n_gpus > 1 else "none",
@@ -251,7 +251,8 @@ def run_ours(args) -> int:
 
     peaks = load_peaks()
     ls = tp.LayerSet.build(PRESET, rank=rank, world=world, bits=4, group_size=128, symmetric=True,
-                           bias=True, device=f"cuda:{local}", seed=0, collective=args.collective)
+                           bias=True, device=f"cuda:{local}", seed=0, collective=args.collective,
+                           concurrent=True)
     torch.manual_seed(0)
     host_x = torch.randn(M_TOKENS, ls.dim).to(torch.bfloat16).pin_memory()
     host_ctx = torch.randn(M_TOKENS, ls.dim).to(torch.bfloat16).pin_memory()
@@ -326,8 +327,9 @@ def run_ours(args) -> int:
     # Same linears with self q/k/v and cross k/v each issued as one N-concatenated launch
     # (same arithmetic per column, but another K-split order, so equal only up to fp32
     # summation order; 7 launches per block instead of 10); reported as an extra.
-    fused = tp.LayerSet(ls.dim, ls.ffn_dim, ls.blocks, rank, world, ls.bits, ls.group_size,
-                        ls.collective, True, [tp.LayerSet._fuse(r) for r in ls.layers])
+    fused = tp.LayerSet(dim=ls.dim, ffn_dim=ls.ffn_dim, blocks=ls.blocks, rank=rank, world=world,
+                        bits=ls.bits, group_size=ls.group_size, collective=ls.collective,
+                        fuse_qkv=True, layers=[tp.LayerSet._fuse(r) for r in ls.layers])
     yf = fused.forward(x, ctx)
     torch.cuda.synchronize()
     fused_ms = None
@@ -353,6 +355,33 @@ def run_ours(args) -> int:
         fused_same = None
         if rank == 0:
             print(f"fused-qkv variant not timed: {exc}", file=sys.stderr)
+
+    # The same 300 launches strictly one after the other (no parallel streams), as an extra.
+    sequential_ms = None
+    try:
+        ls.concurrent = False
+        ys = ls.forward(x, ctx)
+        torch.cuda.synchronize()
+        sgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(sgraph):
+            ys = ls.forward(x, ctx)
+        for _ in range(3):
+            sgraph.replay()
+        barrier()
+        h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        h0.record()
+        for _ in range(args.steps):
+            sgraph.replay()
+        h1.record()
+        barrier()
+        st = torch.tensor([h0.elapsed_time(h1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        sequential_ms = st.item() / args.steps
+    except Exception as exc:  # noqa: BLE001
+        if rank == 0:
+            print(f"sequential variant not timed: {exc}", file=sys.stderr)
+    ls.concurrent = True
 
     total_bytes = torch.tensor([float(ls.weight_bytes)], device="cuda")
     if world > 1:
@@ -392,6 +421,7 @@ def run_ours(args) -> int:
                      "algorithmic_flops_per_launch": flops_per_launch,
                      "us_per_launch": us_per_launch,
                      "frac_hbm": (bytes_per_launch / us_per_launch * 1e-3) / peaks["hbm_gbs"]},
+        "sequential": {"ms_per_step": sequential_ms, "note": "same 300 launches on one stream"},
         "fused_qkv": {"ms_per_step": fused_ms, "launches_per_step": fused.num_gemms,
                       "max_normalised_diff_vs_separate": fused_same,
                       "frac_roofline": None if not fused_ms else roofline_ms / fused_ms},

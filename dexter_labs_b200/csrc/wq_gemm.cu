@@ -867,12 +867,12 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   pl.w_stages = w_stages;
   pl.smem_bytes = static_cast<size_t>(pl.w_stages) * kWStage +
                   static_cast<size_t>(pl.stages) * pl.x_stage_bytes + 1024;
-  // Grid: with an explicit cap, that many CTAs stream-K over all units.  By default one
-  // CTA per tile when the tiles fit the SMs (splitting them through global scratch costs
-  // more than it gains; the launcher splits tiles across a thread-block cluster instead,
-  // where it can), else one CTA per SM, stream-K.
-  int ctas = pl.tiles <= sms ? pl.tiles : sms;
-  if (max_ctas > 0) ctas = max_ctas < sms ? max_ctas : sms;
+  // Grid: `budget` CTAs at most (all SMs unless the caller caps it, e.g. to run several
+  // GEMMs side by side).  One CTA per tile when the tiles fit the budget (splitting them
+  // through global scratch costs more than it gains; the launcher splits tiles across a
+  // thread-block cluster instead, where it can), else `budget` CTAs, stream-K.
+  const int budget = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
+  int ctas = pl.tiles <= budget ? pl.tiles : budget;
   if (ctas > pl.total_units) ctas = pl.total_units;
   pl.ctas = ctas;
   pl.nacc = 2;
@@ -973,15 +973,17 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   // reduces through distributed shared memory.  The cluster size is the largest one for
   // which all clusters are resident at once; the answer is cached per configuration.
   int cluster = 1;
-  if (max_ctas <= 0 && pl.tiles * 2 <= di.sms && pl.units_per_tile >= 2) {
+  const int budget = (max_ctas > 0 && max_ctas < di.sms) ? max_ctas : di.sms;
+  if (pl.tiles * 2 <= budget && pl.units_per_tile >= 2) {
     static thread_local std::unordered_map<long long, int> cache;
     const long long key = (static_cast<long long>(dev) << 48) ^ (static_cast<long long>(pl.tiles) << 28) ^
-                          (static_cast<long long>(pl.units_per_tile) << 8) ^ static_cast<long long>(pl.NU >> 4);
+                          (static_cast<long long>(pl.units_per_tile) << 8) ^ static_cast<long long>(pl.NU >> 4) ^
+                          (static_cast<long long>(budget) << 38);
     auto it = cache.find(key);
     if (it != cache.end()) {
       cluster = it->second;
     } else {
-      int cmax = di.sms / pl.tiles;
+      int cmax = budget / pl.tiles;
       if (cmax > 8) cmax = 8;
       if (cmax > pl.units_per_tile) cmax = pl.units_per_tile;
       for (int c = cmax; c >= 2; --c) {

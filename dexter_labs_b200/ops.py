@@ -124,14 +124,18 @@ def accepts(*args) -> bool:
                 and qweight.dtype == torch.uint8 and qweight.ndim == 2 and scales.ndim == 2)
 
 
-def w4a16(x, qweight, scales, zeros, bias, group_size):
-    """int4 weight-only GEMM, bf16 in / bf16 out."""
-    return _run(4, x, qweight, scales, zeros, bias, group_size)
+def w4a16(x, qweight, scales, zeros, bias, group_size, *, max_ctas: int = 0):
+    """int4 weight-only GEMM, bf16 in / bf16 out.
+
+    ``max_ctas`` (an extension, not part of the reference signature) caps the SMs the
+    launch may use, for callers that run independent GEMMs on parallel streams.
+    """
+    return _run(4, x, qweight, scales, zeros, bias, group_size, max_ctas)
 
 
-def w8a16(x, qweight, scales, zeros, bias, group_size):
-    """int8 weight-only GEMM, bf16 in / bf16 out."""
-    return _run(8, x, qweight, scales, zeros, bias, group_size)
+def w8a16(x, qweight, scales, zeros, bias, group_size, *, max_ctas: int = 0):
+    """int8 weight-only GEMM, bf16 in / bf16 out (``max_ctas``: see :func:`w4a16`)."""
+    return _run(8, x, qweight, scales, zeros, bias, group_size, max_ctas)
 
 
 def dequantize(qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor],

@@ -127,11 +127,11 @@ class ShardedLinear:
         return 2 * m * k * n
 
 
-def _default_gemm(x: torch.Tensor, w: QuantizedWeight) -> torch.Tensor:
+def _default_gemm(x: torch.Tensor, w: QuantizedWeight, max_ctas: int = 0) -> torch.Tensor:
     from . import ops
 
     fn = ops.w4a16 if w.bits == 4 else ops.w8a16
-    return fn(x, w.qweight, w.scales, w.zeros, w.bias, w.group_size)
+    return fn(x, w.qweight, w.scales, w.zeros, w.bias, w.group_size, max_ctas=max_ctas)
 
 
 # (name, input, kind): the ten linears of one DiT block in execution order
@@ -164,21 +164,25 @@ class LayerSet:
     group_size: int = 128
     collective: str = "rs_ag"  # "rs_ag" | "all_reduce"
     fuse_qkv: bool = False     # one launch for self q,k,v and one for cross k,v (N-concatenation)
+    concurrent: bool = False   # independent linears of a block on parallel CUDA streams
     layers: List[List[ShardedLinear]] = field(default_factory=list)
     gemm: GemmFn = _default_gemm
     process_group: Optional[object] = None
     _pad: Dict[Tuple[int, int], torch.Tensor] = field(default_factory=dict)
+    _side: Optional[list] = None
 
     # ------------------------------------------------------------------ build
     @classmethod
     def build(cls, preset: str, *, blocks: Optional[int] = None, rank: int = 0, world: int = 1,
               bits: int = 4, group_size: int = 128, symmetric: bool = True, bias: bool = True,
               device="cuda", seed: int = 0, collective: str = "rs_ag", gemm: GemmFn = _default_gemm,
-              process_group=None, weight_std: float = 0.02, fuse_qkv: bool = False) -> "LayerSet":
+              process_group=None, weight_std: float = 0.02, fuse_qkv: bool = False,
+              concurrent: bool = False) -> "LayerSet":
         dim, ffn, nblocks = PRESETS[preset]
         nblocks = blocks if blocks is not None else nblocks
-        self = cls(dim, ffn, nblocks, rank, world, bits, group_size, collective, fuse_qkv, [], gemm,
-                   process_group)
+        self = cls(dim=dim, ffn_dim=ffn, blocks=nblocks, rank=rank, world=world, bits=bits,
+                   group_size=group_size, collective=collective, fuse_qkv=fuse_qkv,
+                   concurrent=concurrent, layers=[], gemm=gemm, process_group=process_group)
         for blk in range(nblocks):
             row: List[ShardedLinear] = []
             for idx, (name, src, kind) in enumerate(_BLOCK_PLAN):
@@ -266,8 +270,42 @@ class LayerSet:
     def _local_cols(self, full_cols: int) -> Tuple[int, int]:
         return self.rank * full_cols // self.world, (self.rank + 1) * full_cols // self.world
 
+    def _block_forward_concurrent(self, blk: int, x: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
+        """Same linears and data dependencies as :meth:`block_forward`, but the ones that do
+        not depend on each other run side by side: self q, k, v and cross k, v (which only
+        need the block input and the context) start together on five streams, each capped
+        to a fifth of the SMs; o waits for q, k, v; cross o waits for cross q, k, v.  Under
+        CUDA-graph capture this becomes a fork/join graph."""
+        L = {l.name: l for l in self.layers[blk]}
+        g = self.gemm
+        cur = torch.cuda.current_stream()
+        if not hasattr(self, "_side") or self._side is None:
+            self._side = [torch.cuda.Stream() for _ in range(4)]
+            self._sms = torch.cuda.get_device_properties(x.device).multi_processor_count
+        side = self._side
+        share = max(self._sms // 5, 1)
+        for s in side:
+            s.wait_stream(cur)
+        outs = {}
+        for s, (name, inp) in zip(side, (("self_q", x), ("self_k", x), ("cross_k", ctx), ("cross_v", ctx))):
+            with torch.cuda.stream(s):
+                outs[name] = g(inp, L[name].weight, share)
+        v = g(x, L["self_v"].weight, share)
+        cur.wait_stream(side[0])
+        cur.wait_stream(side[1])
+        x = self._reduce(g(self._row_input(v, L["self_o"]), L["self_o"].weight))
+        g(x, L["cross_q"].weight)
+        cur.wait_stream(side[2])
+        cur.wait_stream(side[3])
+        x = self._reduce(g(self._row_input(outs["cross_v"], L["cross_o"]), L["cross_o"].weight))
+        h = g(x, L["ffn_up"].weight)
+        x = self._reduce(g(self._row_input(h, L["ffn_down"]), L["ffn_down"].weight))
+        return x
+
     def block_forward(self, blk: int, x: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
         """x, ctx: ``[M, dim]`` replicated on every rank; returns the new replicated x."""
+        if self.concurrent and not self.fuse_qkv and x.is_cuda:
+            return self._block_forward_concurrent(blk, x, ctx)
         L = {l.name: l for l in self.layers[blk]}
         g = self.gemm
         # self attention: q, k, v column-parallel; the v shard stands in for the attention output

@@ -53,7 +53,8 @@ enum {
  * must be at least dxb_workspace_bytes() and zero-filled once before its first
  * use (the kernel leaves it clean after every normal completion).  Two calls
  * that may overlap on the GPU need different workspaces.
- * `max_ctas` <= 0 lets the library use every SM; a positive value caps the grid.
+ * `max_ctas` <= 0 lets the library use every SM; a positive value caps the grid, so
+ * that several independent GEMMs can run side by side on different streams.
  */
 int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const void* scales,
                 const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
