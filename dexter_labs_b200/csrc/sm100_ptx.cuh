@@ -143,6 +143,20 @@ __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t cluster_addr) {
                : "memory");
   return v;
 }
+__device__ __forceinline__ void st_dsmem_b32x4(uint32_t cluster_addr, uint32_t a, uint32_t b,
+                                               uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a),
+               "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+__device__ __forceinline__ float4 ld_smem_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
 // Hardware barrier over every thread of the cluster; release/acquire at cluster scope,
 // so shared-memory writes made before it are visible to peer CTAs after it.
 __device__ __forceinline__ void cluster_sync_all() {

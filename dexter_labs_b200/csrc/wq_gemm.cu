@@ -85,6 +85,9 @@ struct WqParams {
   int nacc;            // accumulator buffers in TMEM (2 when NU <= 128)
   int group_shift;     // log2(group / 64) when that is a power of two, else -1
   int cluster;         // CTAs per tile (thread-block cluster along x); 1 = no cluster
+  int recv_off;        // cluster mode: byte offset of the receive buffers in shared memory
+  int rows_per;        // cluster mode: token rows each CTA of the cluster reduces
+  int rows_inv;        // ceil(65536 / rows_per): row / rows_per == (row * rows_inv) >> 16
   long long* trace;    // only used when built with -DDXB_TRACE
 };
 
@@ -408,8 +411,11 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         tc_fence_before();
         mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
       } else if (C > 1) {
-        // Cluster mode: park the fp32 sums in this CTA's shared memory (the pipeline
-        // rings are idle by now: every load has been consumed) for the cluster reduce.
+        // Cluster mode: CTA r of the cluster finishes token rows [r*rows_per, (r+1)*rows_per)
+        // of the tile.  Every CTA sends each owner its fp32 partial rows straight from the
+        // accumulator registers into the owner's receive buffer `crank` (distributed shared
+        // memory stores); one cluster barrier later the owner only reads its own memory.
+        const uint32_t recv0 = smem0 + static_cast<uint32_t>(p.recv_off);
         for (int c0 = 0; c0 < p.NU; c0 += 16) {
           uint32_t ra[8], rb[8];
           tmem_ld_16x128b_x4(d_tmem + c0, ra);
@@ -418,12 +424,12 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
           for (int rep = 0; rep < 4; ++rep) {
             const int m = c0 + 4 * rep + c;
-            if (m < p.M)
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
-                               smem0 + static_cast<uint32_t>(m * kTileN + n_local) * 4u),
-                           "r"(ra[2 * rep]), "r"(ra[2 * rep + 1]), "r"(rb[2 * rep]),
-                           "r"(rb[2 * rep + 1])
-                           : "memory");
+            if (m < p.M) {
+              const int owner = (m * p.rows_inv) >> 16;
+              const int row = crank * p.rows_per + (m - owner * p.rows_per);
+              st_dsmem_b32x4(dsmem_addr(recv0 + static_cast<uint32_t>(row * kTileN + n_local) * 4u, owner),
+                             ra[2 * rep], ra[2 * rep + 1], rb[2 * rep], rb[2 * rep + 1]);
+            }
           }
         }
         tc_fence_before();
@@ -663,24 +669,25 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   tc_fence_before();
   __syncthreads();
   if (C > 1) {
-    // Every CTA of the cluster has its partial tile in shared memory: CTA `crank` sums
-    // its share of the token rows over the cluster in rank order (deterministic), adds
-    // the bias and writes bf16.  The second barrier keeps peers' memory alive until read.
+    // After this barrier every partial row of this CTA's share has arrived in its receive
+    // buffers: sum them in rank order (deterministic), add the bias, write bf16.  Nothing
+    // remote is touched any more, so CTAs leave independently.
     cluster_sync_all();
-    const int rows_per = (p.M + C - 1) / C;
-    const int m_lo = crank * rows_per;
-    const int m_hi = (m_lo + rows_per) < p.M ? (m_lo + rows_per) : p.M;
+    const int m_lo = crank * p.rows_per;
+    const int m_hi = (m_lo + p.rows_per) < p.M ? (m_lo + p.rows_per) : p.M;
+    const uint32_t recv0 = smem0 + static_cast<uint32_t>(p.recv_off);
+    const uint32_t src_stride = static_cast<uint32_t>(p.rows_per * kTileN) * 4u;
     const bool has_bias = p.bias != nullptr;
     for (int i = threadIdx.x; i < (m_hi - m_lo) * 32; i += kThreads) {
-      const int m = m_lo + (i >> 5);
+      const int j = i >> 5;
       const int c4 = (i & 31) * 4;
       const int n = ctile * kTileN + c4;
       if (n < p.N) {
-        const uint32_t local = smem0 + static_cast<uint32_t>(m * kTileN + c4) * 4u;
+        const uint32_t a0 = recv0 + static_cast<uint32_t>(j * kTileN + c4) * 4u;
         float4 v[8];
 #pragma unroll
         for (int r = 0; r < 8; ++r)
-          v[r] = r < C ? ld_dsmem_f4(dsmem_addr(local, r)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          v[r] = r < C ? ld_smem_f4(a0 + r * src_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int r = 0; r < 8; ++r) {  // rank order: the sum does not depend on timing
@@ -696,10 +703,9 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           pk.x = cvt_bf16x2(acc.y, acc.x);
           pk.y = cvt_bf16x2(acc.w, acc.z);
         }
-        *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.ldo + n) = pk;
+        *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m_lo + j) * p.ldo + n) = pk;
       }
     }
-    cluster_sync_all();
   }
   if (threadIdx.x == 0) DX_TRACE(7, 0);
   if (warp == 1) tmem_dealloc(tmem0, 512);
@@ -830,7 +836,7 @@ static DeviceInfo& device_info() {
 
 struct Plan {
   int NU, planes, rows, units_per_tile, tiles, total_units, stages, w_stages, x_stage_bytes, ctas,
-      max_slots, nacc;
+      max_slots, nacc, recv_bytes, recv_off;
   size_t smem_bytes;
 };
 
@@ -861,12 +867,21 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   // need the most bytes in flight.  The depth is a multiple of four so that every
   // stage is only ever used by one dequant team, in order.
   pl.stages = kAStages;
-  int w_stages = (kSmemBudget - kAStages * pl.x_stage_bytes) / kWStage;
+  // Launches that may split tiles over a cluster keep room for its receive buffers
+  // (at most NU + 8 token rows of 128 fp32) behind the two rings.
+  const int budget_ctas = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
+  pl.recv_bytes = (pl.tiles * 2 <= budget_ctas && pl.units_per_tile >= 2) ? (pl.NU + 8) * kTileN * 4 : 0;
+  int w_stages = (kSmemBudget - pl.recv_bytes - kAStages * pl.x_stage_bytes) / kWStage;
+  if (pl.recv_bytes > 0 && w_stages < 2 * kAStages) {
+    // not enough room for a useful weight ring next to the receive buffers: no cluster split
+    pl.recv_bytes = 0;
+    w_stages = (kSmemBudget - kAStages * pl.x_stage_bytes) / kWStage;
+  }
   w_stages = (w_stages / kAStages) * kAStages;
   if (w_stages > kMaxWStages) w_stages = kMaxWStages;
   pl.w_stages = w_stages;
-  pl.smem_bytes = static_cast<size_t>(pl.w_stages) * kWStage +
-                  static_cast<size_t>(pl.stages) * pl.x_stage_bytes + 1024;
+  pl.recv_off = pl.w_stages * kWStage + pl.stages * pl.x_stage_bytes;
+  pl.smem_bytes = static_cast<size_t>(pl.recv_off) + pl.recv_bytes + 1024;
   // Grid: `budget` CTAs at most (all SMs unless the caller caps it, e.g. to run several
   // GEMMs side by side).  One CTA per tile when the tiles fit the budget (splitting them
   // through global scratch costs more than it gains; the launcher splits tiles across a
@@ -974,7 +989,7 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   // which all clusters are resident at once; the answer is cached per configuration.
   int cluster = 1;
   const int budget = (max_ctas > 0 && max_ctas < di.sms) ? max_ctas : di.sms;
-  if (pl.tiles * 2 <= budget && pl.units_per_tile >= 2) {
+  if (pl.recv_bytes > 0 && pl.tiles * 2 <= budget && pl.units_per_tile >= 2) {
     static thread_local std::unordered_map<long long, int> cache;
     const long long key = (static_cast<long long>(dev) << 48) ^ (static_cast<long long>(pl.tiles) << 28) ^
                           (static_cast<long long>(pl.units_per_tile) << 8) ^ static_cast<long long>(pl.NU >> 4) ^
@@ -1010,6 +1025,9 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
     }
   }
   p.cluster = cluster;
+  p.recv_off = pl.recv_off;
+  p.rows_per = (M + cluster - 1) / cluster;
+  p.rows_inv = (65536 + p.rows_per - 1) / p.rows_per;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(cluster > 1 ? pl.tiles * cluster : pl.ctas);
