@@ -1098,8 +1098,11 @@ int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const
                        (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 8 == 0) &&
                        (reinterpret_cast<uintptr_t>(out) % 8 == 0) && (ldo % 4 == 0) &&
                        (bits != 4 || (K / 2) % 8 == 0);
-  // Token blocks of at most 128 rows per launch (the UMMA N of one accumulator).
-  const int chunk = M <= 128 ? M : 128;
+  // Token blocks of at most 128 rows per launch (the UMMA N of one accumulator); 96 when the
+  // weight has so few tiles that the launch splits them over clusters, whose receive buffers
+  // only fit next to the activation ring up to 96 tokens.
+  int chunk = M <= 128 ? M : 128;
+  if (M > 128 && ((N + kTileN - 1) / kTileN) * 2 <= device_info().sms) chunk = 96;
   for (int m0 = 0; m0 < M; m0 += chunk) {
     const int mc = (M - m0) < chunk ? (M - m0) : chunk;
     const char* xc = static_cast<const char*>(x) + static_cast<long long>(m0) * ldx * 2;

@@ -170,6 +170,7 @@ class LayerSet:
     process_group: Optional[object] = None
     _pad: Dict[Tuple[int, int], torch.Tensor] = field(default_factory=dict)
     _side: Optional[list] = None
+    _sms: int = 0
 
     # ------------------------------------------------------------------ build
     @classmethod
@@ -279,7 +280,7 @@ class LayerSet:
         L = {l.name: l for l in self.layers[blk]}
         g = self.gemm
         cur = torch.cuda.current_stream()
-        if not hasattr(self, "_side") or self._side is None:
+        if self._side is None:
             self._side = [torch.cuda.Stream() for _ in range(4)]
             self._sms = torch.cuda.get_device_properties(x.device).multi_processor_count
         side = self._side
