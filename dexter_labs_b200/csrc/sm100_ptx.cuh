@@ -128,6 +128,16 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// ------------------------------------------- programmatic dependent launch --
+// A kernel launched with programmatic stream serialisation may start while the kernel
+// before it in the stream is still running.  `pdl_wait` blocks until that kernel has
+// finished and its writes are visible; `pdl_launch_dependents` lets the NEXT kernel in
+// the stream start early.  Both are no-ops for ordinary launches.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ------------------------------------------------- thread-block clusters --
 // Address of the same shared-memory location in CTA `rank` of this cluster.
 __device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t rank) {

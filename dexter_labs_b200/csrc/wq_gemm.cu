@@ -213,6 +213,9 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem0 = tmem_base_s;
+  // The next kernel of the stream may start now: its weight loads and conversion do not
+  // depend on this kernel; it waits (pdl_wait) before it touches activations or outputs.
+  pdl_launch_dependents();
 
   // This CTA's contiguous range of (tile, unit) work.
   // Cluster mode: the `cluster` CTAs of one cluster share one tile, each taking a
@@ -268,6 +271,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     __syncwarp();
   } else if (warp == 2) {
     // ============================================== TMA producer: activations
+    // Activations may be the output of the previous kernel in the stream.
+    pdl_wait();
     {
       int ku = ku_begin, t = 0;
       uint32_t ph = 0;
@@ -356,6 +361,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // Accumulator lane 32q + 8b + g holds weight column 32q + 4g + b (see the
     // dequant mapping), so the 16x128b load shape hands thread (g, c) the four
     // consecutive columns 4g..4g+3 of token 4*rep + c: one 8-byte store each.
+    pdl_wait();  // outputs / scratch may still be in use by the previous kernel
     const int q = warp & 3;
     const int etid = (warp - 4) * 32 + lane;
     const int c = lane & 3;
@@ -673,6 +679,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // buffers: sum them in rank order (deterministic), add the bias, write bf16.  Nothing
     // remote is touched any more, so CTAs leave independently.
     cluster_sync_all();
+    pdl_wait();
     const int m_lo = crank * p.rows_per;
     const int m_hi = (m_lo + p.rows_per) < p.M ? (m_lo + p.rows_per) : p.M;
     const uint32_t recv0 = smem0 + static_cast<uint32_t>(p.recv_off);
@@ -709,7 +716,10 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   }
   if (threadIdx.x == 0) DX_TRACE(7, 0);
   if (warp == 1) tmem_dealloc(tmem0, 512);
-  if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, DXB_ERR_KERNEL_TIMEOUT);
+  if (threadIdx.x == 0 && abort_flag) {
+    pdl_wait();
+    atomicExch(p.status, DXB_ERR_KERNEL_TIMEOUT);
+  }
 }
 
 // --------------------------------------------- dense dequantised weight dump
@@ -832,6 +842,15 @@ static DeviceInfo& device_info() {
   DeviceInfo& d = infos[dev];
   if (d.sms == 0) cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
   return d;
+}
+
+// Programmatic dependent launch is on unless DEXTER_B200_PDL=0.
+static bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("DEXTER_B200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 struct Plan {
@@ -1034,15 +1053,24 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = pl.smem_bytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int nattr = 0;
   if (cluster > 1) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cluster;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[nattr].id = cudaLaunchAttributeClusterDimension;
+    attr[nattr].val.clusterDim.x = cluster;
+    attr[nattr].val.clusterDim.y = 1;
+    attr[nattr].val.clusterDim.z = 1;
+    ++nattr;
   }
+  if (pdl_enabled()) {
+    // Let this launch begin while the previous kernel of the stream drains: the kernel
+    // itself waits (griddepcontrol.wait) before touching anything that kernel may produce.
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = nattr;
   if (cudaLaunchKernelEx(&cfg, kernel, tq, tx, p) != cudaSuccess) {
     cudaGetLastError();
     return DXB_ERR_CUDA;
