@@ -209,3 +209,46 @@ def test_one_block_layer_set_matches_oracle_chain(d, oracle):
     want = ls.forward(x, ctx)
     assert err(got.float(), want.float()) < TOL
     assert ls.num_gemms == 10
+
+
+# ------------------------------------------------- launch regimes of the tensor-core kernel
+@pytest.mark.parametrize("m,k,n,nbits,max_ctas,why", [
+    (83, 512, 20480, 4, 0, "160 tiles > SMs: stream-K with global partials and counters"),
+    (83, 3072, 3072, 4, 7, "explicit cap below the tile count: stream-K, several tiles per CTA"),
+    (83, 3072, 3072, 4, 1, "one CTA walks every tile"),
+    (64, 3072, 3072, 8, 60, "cap that still allows a cluster of 2 per tile"),
+    (83, 3072, 3072, 4, 0, "24 tiles: cluster split with the DSMEM reduce"),
+    (83, 14336, 3072, 4, 0, "row-parallel shape, 112 units per tile, cluster split"),
+    (128, 3072, 3072, 4, 0, "128 tokens: no room for cluster buffers, one CTA per tile"),
+    (83, 3072, 14336, 4, 0, "112 tiles: one CTA per tile"),
+])
+def test_launch_regimes(m, k, n, nbits, max_ctas, why, d, oracle):
+    group = 128
+    x, qw, b = seeded(d, m, k, n, nbits, group, False, seed=k + n + max_ctas, bias=True)
+    xg, bg = x.cuda(), b.cuda()
+    fn = d.w4a16 if nbits == 4 else d.w8a16
+    y = fn(xg, qw.qweight, qw.scales, qw.zeros, bg, group, max_ctas=max_ctas)
+    want = oracle.torch_wq_gemm(xg, qw.qweight, qw.scales, qw.zeros, bg, group, nbits)
+    assert err(y.float(), want.float()) < TOL, why
+    again = fn(xg, qw.qweight, qw.scales, qw.zeros, bg, group, max_ctas=max_ctas)
+    assert torch.equal(again.view(torch.int16), y.view(torch.int16)), "not deterministic: " + why
+    assert d.ops.last_status() == 0
+
+
+def test_back_to_back_launches_with_dependent_launch(d, oracle):
+    # consecutive GEMMs on one stream overlap (programmatic dependent launch); a chain in
+    # which each GEMM consumes the previous output must still see finished inputs
+    _, q1, _ = seeded(d, 83, 3072, 3072, 4, 128, True, seed=31)
+    _, q2, _ = seeded(d, 83, 3072, 3072, 4, 128, True, seed=32)
+    torch.manual_seed(5)
+    x = torch.randn(83, 3072, device="cuda").to(torch.bfloat16)
+    got = x
+    for _ in range(4):
+        got = d.w4a16(d.w4a16(got, q1.qweight, q1.scales, None, None, 128),
+                      q2.qweight, q2.scales, None, None, 128)
+    want = x
+    for _ in range(4):
+        want = oracle.torch_wq_gemm(oracle.torch_wq_gemm(want, q1.qweight, q1.scales, None, None, 128, 4),
+                                    q2.qweight, q2.scales, None, None, 128, 4)
+    assert err(got.float(), want.float()) < 5 * TOL  # eight chained GEMMs accumulate rounding
+    assert torch.isfinite(got.float()).all()
