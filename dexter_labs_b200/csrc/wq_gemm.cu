@@ -58,6 +58,7 @@ constexpr int kAStages = 4;      // dequantised-tile ring in TMEM
 constexpr int kACol0 = 256;      // TMEM column where that ring starts
 constexpr int kThreads = 768;    // 24 warps
 constexpr int kDequantThreads = 128;  // one team
+constexpr int kTeamWarps = kDequantThreads / 32;
 constexpr int kEpilogueThreads = 128;
 constexpr int kSmemBudget = 227 * 1024 - 4096;
 constexpr int kMaxTiles = 16384;  // tile counters reserved in every workspace
@@ -165,10 +166,12 @@ constexpr int kBarFullW = 0, kBarEmptyW = 16, kBarReady = 32, kBarFree = 36, kBa
 
 __device__ __forceinline__ uint32_t bar_count(int i) {
   if (i < kBarEmptyW) return 1;                    // full_w: producer's expect_tx
-  if (i < kBarReady) return kDequantThreads;       // empty_w: one dequant team
-  if (i < kBarFree) return kDequantThreads + 1;    // ready: team + activation producer
+  // One arrival per WARP, not per thread: 128 arrivals on one barrier word serialise in
+  // the shared-memory atomic unit and put ~500 cycles on every hand-over.
+  if (i < kBarReady) return kTeamWarps;            // empty_w: the four warps of one team
+  if (i < kBarFree) return kTeamWarps + 1;         // ready: team warps + activation producer
   if (i < kBarAccEmpty) return 1;                  // free, acc_full: one tcgen05.commit
-  return kEpilogueThreads;                         // acc_empty
+  return kEpilogueThreads / 32;                    // acc_empty: the four epilogue warps
 }
 
 template <int BITS, bool HAS_ZERO>
@@ -415,7 +418,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           }
         }
         tc_fence_before();
-        mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
       } else if (C > 1) {
         // Cluster mode: CTA r of the cluster finishes token rows [r*rows_per, (r+1)*rows_per)
         // of the tile.  Every CTA sends each owner its fp32 partial rows straight from the
@@ -439,7 +443,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           }
         }
         tc_fence_before();
-        mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
       } else {
         // Partial tile: park the fp32 sums, then whoever completes the tile reduces.
         const int c_first = owner_of(static_cast<long long>(tile) * U, TU, G);
@@ -463,7 +468,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           }
         }
         tc_fence_before();
-        mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
         __threadfence();
         named_bar_sync(1, kEpilogueThreads);
         if (etid == 0) {
@@ -602,7 +608,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         w0[sl] = lds32(wsrc + off0 + sl * 1024);
         w1[sl] = lds32(wsrc + off1 + sl * 1024);
       }
-      mbar_arrive(bar0 + 8 * (kBarEmptyW + s));  // packed stage is in registers now
+      __syncwarp();  // every lane has its words in registers
+      if (lane == 0) mbar_arrive(bar0 + 8 * (kBarEmptyW + s));
       ok = mbar_wait(a_empty_bar, aph ^ 1u, abortp);
       if (!ok) break;
       if (q == 0 && lane == 0) DX_TRACE(6, (u - u_begin));
@@ -662,7 +669,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(a_full_bar);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a_full_bar);
       if (q == 0 && lane == 0) DX_TRACE(2, (u - u_begin));
       aph ^= 1u;
       s += kAStages;
