@@ -252,3 +252,56 @@ def test_back_to_back_launches_with_dependent_launch(d, oracle):
                                     q2.qweight, q2.scales, None, None, 128, 4)
     assert err(got.float(), want.float()) < 5 * TOL  # eight chained GEMMs accumulate rounding
     assert torch.isfinite(got.float()).all()
+
+
+# ------------------------------------------- 14B-shaped linears at M = 913 (BASELINE config 5)
+@pytest.mark.parametrize("shape", [("qkv_like", 5120, 5120), ("up", 5120, 13824), ("down", 13824, 5120)])
+def test_14b_shapes_m913(shape, d, oracle):
+    _, k, n = shape
+    x, qw, b = seeded(d, 913, k, n, 4, 128, True, seed=k + n, bias=True)
+    xg, bg = x.cuda(), b.cuda()
+    y = run(d, 4, xg, qw, bg)
+    want = oracle.torch_wq_gemm(xg, qw.qweight, qw.scales, qw.zeros, bg, 128, 4)
+    assert err(y.float(), want.float()) < TOL
+    dense = d.dequantize(qw.qweight, qw.scales, qw.zeros, 128, 4)
+    assert torch.equal(dense.view(torch.int16),
+                       oracle.torch_dequantize(qw.qweight, qw.scales, qw.zeros, 128, 4).view(torch.int16))
+    assert d.ops.last_status() == 0
+
+
+# -------------------------------------------------- shapes a tensor-parallel shard produces
+@pytest.mark.parametrize("m,k,n,nbits", [
+    (83, 384, 3072, 4),     # 5B o-projection, K sharded 8 ways: 3 units per tile (odd)
+    (83, 1792, 3072, 4),    # 5B FFN-down, K sharded 8 ways
+    (83, 3072, 384, 4),     # 5B q/k/v, N sharded 8 ways: 3 tiles
+    (83, 3072, 1792, 4),    # 5B FFN-up, N sharded 8 ways: 14 tiles
+    (83, 768, 1536, 8),     # int8, per-channel, 2-way shards
+])
+def test_shard_sized_shapes(m, k, n, nbits, d, oracle):
+    group = 128 if nbits == 4 else k
+    x, qw, b = seeded(d, m, k, n, nbits, group, False, seed=k * 7 + n, bias=True)
+    xg, bg = x.cuda(), b.cuda()
+    y = run(d, nbits, xg, qw, bg)
+    want = oracle.c_wq_gemm(bits(x), qw.qweight.cpu().numpy(), bits(qw.scales), bits(qw.zeros),
+                            bits(b), group, nbits)
+    assert err(y.cpu().float(), torch.from_numpy(oracle.bf16_bits_to_f32(want))) < TOL
+    assert d.ops.last_status() == 0
+
+
+def test_two_streams_do_not_share_scratch(d, oracle):
+    # stream-K launches keep their partial sums in a per-stream workspace
+    x, qw, _ = seeded(d, 83, 512, 20480, 4, 128, True, seed=77)
+    xg = x.cuda()
+    want = run(d, 4, xg, qw)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    outs = []
+    for _ in range(3):
+        with torch.cuda.stream(s1):
+            a = run(d, 4, xg, qw)
+        with torch.cuda.stream(s2):
+            b = run(d, 4, xg, qw)
+        outs += [a, b]
+    torch.cuda.synchronize()
+    for o in outs:
+        assert torch.equal(o.view(torch.int16), want.view(torch.int16))
