@@ -18,8 +18,22 @@ ERRORS = {
     -8: "DXB_ERR_KERNEL_TIMEOUT", -9: "DXB_ERR_SCRATCH_LIMIT",
 }
 
+DXB_CHAIN_MAX = 32
+
+
+class ChainItem(ctypes.Structure):
+    """``dxb_chain_item`` of include/dexter_b200.h."""
+    _fields_ = [("x", c_void_p), ("ldx", c_int64), ("qweight", c_void_p), ("scales", c_void_p),
+                ("zeros", c_void_p), ("bias", c_void_p), ("out", c_void_p), ("ldo", c_int64),
+                ("M", c_int), ("N", c_int), ("K", c_int), ("group_size", c_int),
+                ("depends_on", c_int)]
+
+
 # name -> (restype, argtypes); one entry per symbol declared in include/dexter_b200.h
 SIGNATURES = {
+    "dxb_chain_workspace_bytes": (c_size_t, [c_int, ctypes.POINTER(ChainItem), c_int, c_int]),
+    "dxb_wq_gemm_chain": (c_int, [c_int, ctypes.POINTER(ChainItem), c_int, c_void_p, c_size_t,
+                                  c_int, c_void_p]),
     "dxb_wq_gemm": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
                             c_int, c_void_p]),

@@ -2,7 +2,7 @@
 
 ``python dexter_labs_b200/build.py`` (run as a script, so the package -- which loads the
 library on import -- is not imported first) or :func:`build` runs nvcc on
-``csrc/wq_gemm.cu`` and leaves the shared library next to this file, where
+``csrc/*.cu`` and leaves the shared library next to this file, where
 :mod:`dexter_labs_b200._lib` loads it.  nvcc cross-compiles without a GPU.
 """
 from __future__ import annotations
@@ -14,8 +14,8 @@ import sys
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
-SOURCES = [PKG_DIR / "csrc" / "wq_gemm.cu"]
-HEADERS = [PKG_DIR / "csrc" / "sm100_ptx.cuh", PKG_DIR.parent / "include" / "dexter_b200.h"]
+SOURCES = [PKG_DIR / "csrc" / "wq_gemm.cu", PKG_DIR / "csrc" / "wq_chain.cu"]
+HEADERS = [PKG_DIR / "csrc" / "sm100_ptx.cuh", PKG_DIR / "csrc" / "wq_common.cuh", PKG_DIR.parent / "include" / "dexter_b200.h"]
 LIB_PATH = PKG_DIR / "libdexter_b200.so"
 
 NVCC_FLAGS = [

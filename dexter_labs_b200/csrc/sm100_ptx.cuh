@@ -83,6 +83,48 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// Cluster-scope variants: another CTA of the cluster arrives on a barrier in THIS CTA's
+// shared memory after writing this CTA's shared memory (st.shared::cluster).  The arrive
+// releases, the wait acquires, both at cluster scope, so those writes are visible to the
+// waiter.  `cluster_bar` is a shared::cluster address (see dsmem_addr).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_parked_cluster(uint32_t bar, uint32_t parity,
+                                                             uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
+                                                  volatile int* abort_flag) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  for (uint32_t tries = 0; tries < kWaitTries; ++tries) {
+    if (mbar_try_wait_parked_cluster(bar, parity, kWaitHintNs)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
 // --------------------------------------------------------------------- TMA --
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
@@ -126,6 +168,31 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
 }
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// Orders this thread's generic-proxy accesses (ordinary loads and stores) against
+// async-proxy accesses (TMA) to the same global or shared memory, in both directions.
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+// -------------------------------------------------- flags in global memory --
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait (one calling thread) until *p >= target.  Gives up after about a second
+// or as soon as another role of the CTA has given up, setting the CTA's abort flag.
+constexpr uint32_t kFlagTries = 4000000u;
+__device__ __forceinline__ bool wait_flag_ge(const int* p, int target, volatile int* abort_flag) {
+  for (uint32_t tries = 0; tries < kFlagTries; ++tries) {
+    if (ld_acquire_gpu(p) >= target) return true;
+    if (*abort_flag) return false;
+    __nanosleep(tries < 64 ? 32 : 256);
+  }
+  *abort_flag = 1;
+  return false;
 }
 
 // ------------------------------------------- programmatic dependent launch --

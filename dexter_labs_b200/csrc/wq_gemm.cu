@@ -27,18 +27,7 @@
 // ranges, one per CTA; a tile shared by several CTAs is finished by whichever CTA
 // arrives last (no CTA ever waits for another one), summing the partials in a
 // fixed order so results are deterministic.
-#include <cstdint>
-#include <cstdio>
-#include <cstring>
-#include <cstdlib>
-#include <mutex>
-#include <unordered_map>
-#include <cuda.h>
-#include <cuda_bf16.h>
-#include <cuda_runtime.h>
-
-#include "../../include/dexter_b200.h"
-#include "sm100_ptx.cuh"
+#include "wq_common.cuh"
 
 namespace dx {
 #ifdef DXB_TRACE
@@ -47,21 +36,6 @@ namespace dx {
 #define DX_TRACE(role, i) do { } while (0)
 #endif
 
-// ------------------------------------------------------------------ constants
-constexpr int kTileN = 128;      // weight columns per tile (UMMA M)
-constexpr int kUnitRows = 64;    // packed rows per pipeline unit
-constexpr int kQBytes = kTileN * kUnitRows;  // 8192
-constexpr int kWStage = kQBytes;
-constexpr int kMaxStages = 8;    // activation ring
-constexpr int kMaxWStages = 16;  // packed-weight ring; always a multiple of kAStages
-constexpr int kAStages = 4;      // dequantised-tile ring in TMEM
-constexpr int kACol0 = 256;      // TMEM column where that ring starts
-constexpr int kThreads = 768;    // 24 warps
-constexpr int kDequantThreads = 128;  // one team
-constexpr int kTeamWarps = kDequantThreads / 32;
-constexpr int kEpilogueThreads = 128;
-constexpr int kSmemBudget = 227 * 1024 - 4096;
-constexpr int kMaxTiles = 16384;  // tile counters reserved in every workspace
 
 struct WqParams {
   const __nv_bfloat16* scales;
@@ -75,7 +49,9 @@ struct WqParams {
   int M, N, K, group;
   int NU;              // tokens padded to a multiple of 16: the UMMA N
   int units_per_tile;  // packed rows / 64
-  int tiles;           // ceil(N / 128)
+  int tiles;           // ceil(N / 128) x token blocks: tile t is token block t / tiles_n,
+                       // weight columns 128 * (t % tiles_n)
+  int tiles_n;         // ceil(N / 128)
   int total_units;
   int half_k;          // int4: K/2 (first activation column of the high-nibble plane)
   int stages;          // activation (X) ring depth
@@ -92,87 +68,6 @@ struct WqParams {
   long long* trace;    // only used when built with -DDXB_TRACE
 };
 
-// -------------------------------------------------------------- dequant math
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t d;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-  return d;
-}
-__device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-__device__ __forceinline__ uint32_t cvt_bf16x2(float hi, float lo) {
-  uint32_t d;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-  return d;
-}
-// Two nibbles (bits 0..3 and 16..19 of `w`) -> two bf16 weights.  OR-ing a nibble
-// into the mantissa of 0x4300 gives 128 + q exactly; `zero2` holds 128 + zero
-// point in both halves (0x4308 = 136.0 for the symmetric midpoint 8), so the
-// subtract is exact and the multiply is the only rounding.
-__device__ __forceinline__ uint32_t deq4(uint32_t w, uint32_t zero2, uint32_t scale2) {
-  const uint32_t v = (w & 0x000F000Fu) | 0x43004300u;
-  return mul_bf16x2(sub_bf16x2(v, zero2), scale2);
-}
-// One byte -> fp32 by bit pattern: 0x4B0000qq = 8388608 + q.  `cz` = 8388608 +
-// zero point; subtract and multiply are both exact in fp32 (8-bit x 8-bit
-// significands), so the later cvt.rn to bf16 is the only rounding.
-__device__ __forceinline__ float deq8(uint32_t word, uint32_t byte_sel, float cz, float scale) {
-  const float f = __uint_as_float(prmt(word, 0x4B000000u, 0x7650u + byte_sel));
-  return (f - cz) * scale;
-}
-__device__ __forceinline__ uint32_t dup_lo(uint32_t w) { return prmt(w, w, 0x1010u); }
-__device__ __forceinline__ uint32_t dup_hi(uint32_t w) { return prmt(w, w, 0x3232u); }
-__device__ __forceinline__ float bf16lo_f32(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf16hi_f32(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
-
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
-  return v;
-}
-__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
-// First unit of CTA c and the CTA that owns unit u, for `total` units cut into
-// `ctas` contiguous ranges.
-__host__ __device__ inline long long range_begin(long long c, long long total, long long ctas) {
-  return c * total / ctas;
-}
-__host__ __device__ inline int owner_of(long long u, long long total, long long ctas) {
-  return static_cast<int>(((u + 1) * ctas - 1) / total);
-}
-
-// ----------------------------------------------------------------- the kernel
-// Barrier slots in shared memory.
-// ready[t]: unit slot t has its activations in shared memory (TMA bytes) AND its
-// dequantised weights in TMEM (128 arrivals of one team); free[t]: the MMAs that
-// read slot t are done (one tcgen05.commit), so both may be overwritten.
-constexpr int kBarFullW = 0, kBarEmptyW = 16, kBarReady = 32, kBarFree = 36, kBarAccFull = 40,
-              kBarAccEmpty = 42, kNumBars = 44;
-
-__device__ __forceinline__ uint32_t bar_count(int i) {
-  if (i < kBarEmptyW) return 1;                    // full_w: producer's expect_tx
-  // One arrival per WARP, not per thread: 128 arrivals on one barrier word serialise in
-  // the shared-memory atomic unit and put ~500 cycles on every hand-over.
-  if (i < kBarReady) return kTeamWarps;            // empty_w: the four warps of one team
-  if (i < kBarFree) return kTeamWarps + 1;         // ready: team warps + activation producer
-  if (i < kBarAccEmpty) return 1;                  // free, acc_full: one tcgen05.commit
-  return kEpilogueThreads / 32;                    // acc_empty: the four epilogue warps
-}
 
 template <int BITS, bool HAS_ZERO>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -247,6 +142,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const int pi = warp == 0 ? 0 : 1;
       int tile = tile_begin, ku = ku_begin + pi, s = pi;
       while (ku >= U) { ku -= U; ++tile; }
+      int ntile = tile % p.tiles_n;
       uint32_t ph = 0;
       int issued = 0;
       bool ok = true;
@@ -256,14 +152,14 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (elect_one()) {
           const uint32_t fw = bar0 + 8 * (kBarFullW + s);
           mbar_expect_tx(fw, kQBytes);
-          tma_load_2d(w_ring + s * kWStage, &tm_q, fw, tile * kTileN, ku * kUnitRows);
+          tma_load_2d(w_ring + s * kWStage, &tm_q, fw, ntile * kTileN, ku * kUnitRows);
         }
         __syncwarp();
         ++issued;
         s += 2;
         if (s >= SW) { s -= SW; ph ^= 1u; }
         ku += 2;
-        while (ku >= U) { ku -= U; ++tile; }
+        while (ku >= U) { ku -= U; ++tile; if (++ntile == p.tiles_n) ntile = 0; }
       }
       if (!ok && lane == 0) {
         // Leaving early: let the copies already issued land before the CTA exits.
@@ -278,6 +174,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     pdl_wait();
     {
       int ku = ku_begin, t = 0;
+      int ntile = tile_begin % p.tiles_n;
+      int row0 = (tile_begin / p.tiles_n) * 128;  // first token row of the tile's token block
       uint32_t ph = 0;
       int issued = 0;
       bool ok = true;
@@ -289,14 +187,17 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           const uint32_t rb = bar0 + 8 * (kBarReady + t);
           mbar_expect_tx(rb, x_bytes);
           if (BITS == 4)
-            tma_load_3d(x_ring + t * p.x_stage_bytes, &tm_x, rb, ku * kUnitRows, 0, 0);
+            tma_load_3d(x_ring + t * p.x_stage_bytes, &tm_x, rb, ku * kUnitRows, row0, 0);
           else
-            tma_load_2d(x_ring + t * p.x_stage_bytes, &tm_x, rb, ku * kUnitRows, 0);
+            tma_load_2d(x_ring + t * p.x_stage_bytes, &tm_x, rb, ku * kUnitRows, row0);
         }
         __syncwarp();
         ++issued;
         if (++t == kAStages) { t = 0; ph ^= 1u; }
-        if (++ku == U) ku = 0;
+        if (++ku == U) {
+          ku = 0;
+          if (++ntile == p.tiles_n) { ntile = 0; row0 += 128; }
+        }
       }
       if (!ok && lane == 0) {
         // Leaving early: give copies already issued time to land before the CTA exits.
@@ -379,19 +280,25 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const int left = u_end - u;
       const int nun = left < (U - ku0) ? left : (U - ku0);
       const bool whole = (nun == U);
+      const int tblock = tile / p.tiles_n;           // token block of this tile
+      const int ntile = tile - tblock * p.tiles_n;   // its 128 weight columns
+      const int row0 = tblock * 128;
+      const int m_rows = (p.M - row0) < 128 ? (p.M - row0) : 128;  // token rows in this block
+      const int n = ntile * kTileN + n_local;
+      const bool n_ok = n < p.N;
+      // The bias does not depend on the accumulator: fetch it before waiting, so that its
+      // latency is not added to the tail of the tile.
+      float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (whole && has_bias && n_ok) {
+        const uint2 bb = __ldg(reinterpret_cast<const uint2*>(p.bias + n));
+        bias4[0] = bf16lo_f32(bb.x); bias4[1] = bf16hi_f32(bb.x);
+        bias4[2] = bf16lo_f32(bb.y); bias4[3] = bf16hi_f32(bb.y);
+      }
       ok = mbar_wait(bar0 + 8 * (kBarAccFull + b), accph, abortp);
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_addr(tmem0 + b * p.NU, 32 * q, 0);
-      const int n = tile * kTileN + n_local;
-      const bool n_ok = n < p.N;
       if (whole) {
-        float bias4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (has_bias && n_ok) {
-          const uint2 bb = *reinterpret_cast<const uint2*>(p.bias + n);
-          bias4[0] = bf16lo_f32(bb.x); bias4[1] = bf16hi_f32(bb.x);
-          bias4[2] = bf16lo_f32(bb.y); bias4[3] = bf16hi_f32(bb.y);
-        }
         for (int c0 = 0; c0 < p.NU; c0 += 16) {
           uint32_t ra[8], rb[8];
           tmem_ld_16x128b_x4(d_tmem + c0, ra);
@@ -400,7 +307,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
           for (int rep = 0; rep < 4; ++rep) {
             const int m = c0 + 4 * rep + c;
-            if (n_ok && m < p.M) {
+            if (n_ok && m < m_rows) {
               const float f[4] = {__uint_as_float(ra[2 * rep]), __uint_as_float(ra[2 * rep + 1]),
                                   __uint_as_float(rb[2 * rep]), __uint_as_float(rb[2 * rep + 1])};
               uint2 pk;
@@ -413,7 +320,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                 pk.x = cvt_bf16x2(f[1], f[0]);
                 pk.y = cvt_bf16x2(f[3], f[2]);
               }
-              *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.ldo + n) = pk;
+              *reinterpret_cast<uint2*>(p.out + static_cast<long long>(row0 + m) * p.ldo + n) = pk;
             }
           }
         }
@@ -461,7 +368,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
           for (int rep = 0; rep < 4; ++rep) {
             const int m = c0 + 4 * rep + c;
-            if (m < p.M)
+            if (m < m_rows)
               __stcg(reinterpret_cast<float4*>(ws + m * kTileN + n_local),
                      make_float4(__uint_as_float(ra[2 * rep]), __uint_as_float(ra[2 * rep + 1]),
                                  __uint_as_float(rb[2 * rep]), __uint_as_float(rb[2 * rep + 1])));
@@ -485,14 +392,14 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           // slot order, so the result does not depend on which CTA arrives last.
           const int nslots = c_last - c_first + 1;
           const int col4 = (etid & 31) * 4;
-          const int nn = tile * kTileN + col4;
+          const int nn = ntile * kTileN + col4;
           if (nn < p.N) {
             float bias4[4] = {0.f, 0.f, 0.f, 0.f};
             if (has_bias) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) bias4[j] = __bfloat162float(p.bias[nn + j]);
             }
-            for (int m0 = etid >> 5; m0 < p.M; m0 += 16) {
+            for (int m0 = etid >> 5; m0 < m_rows; m0 += 16) {
               float4 acc[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -501,7 +408,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   const int m = m0 + 4 * j;
-                  v[j] = m < p.M ? __ldcg(reinterpret_cast<const float4*>(
+                  v[j] = m < m_rows ? __ldcg(reinterpret_cast<const float4*>(
                                        tile_ws + sl * slot_elems + m * kTileN + col4))
                                  : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
@@ -513,7 +420,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int m = m0 + 4 * j;
-                if (m < p.M) {
+                if (m < m_rows) {
                   uint2 pk;
                   if (has_bias) {
                     const uint32_t r01 = cvt_bf16x2(acc[j].y, acc[j].x);
@@ -524,7 +431,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                     pk.x = cvt_bf16x2(acc[j].y, acc[j].x);
                     pk.y = cvt_bf16x2(acc[j].w, acc[j].z);
                   }
-                  *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.ldo + nn) = pk;
+                  *reinterpret_cast<uint2*>(p.out + static_cast<long long>(row0 + m) * p.ldo + nn) = pk;
                 }
               }
             }
@@ -578,7 +485,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     uint2 sc[PLANES], zr[PLANES], sc_nx[PLANES], zr_nx[PLANES];
     const int n4_stride = p.N >> 2;  // uint2 (4 x bf16) elements per scale row
     auto load_sz = [&](int tile_, int ku_, uint2 (&s_out)[PLANES], uint2 (&z_out)[PLANES]) {
-      const int n = tile_ * kTileN + n_local;
+      const int n = (tile_ % p.tiles_n) * kTileN + n_local;
       const bool in = n < p.N && tile_ < p.tiles;
 #pragma unroll
       for (int pl = 0; pl < PLANES; ++pl) {
@@ -686,18 +593,26 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // After this barrier every partial row of this CTA's share has arrived in its receive
     // buffers: sum them in rank order (deterministic), add the bias, write bf16.  Nothing
     // remote is touched any more, so CTAs leave independently.
-    cluster_sync_all();
-    pdl_wait();
     const int m_lo = crank * p.rows_per;
     const int m_hi = (m_lo + p.rows_per) < p.M ? (m_lo + p.rows_per) : p.M;
     const uint32_t recv0 = smem0 + static_cast<uint32_t>(p.recv_off);
     const uint32_t src_stride = static_cast<uint32_t>(p.rows_per * kTileN) * 4u;
     const bool has_bias = p.bias != nullptr;
-    for (int i = threadIdx.x; i < (m_hi - m_lo) * 32; i += kThreads) {
-      const int j = i >> 5;
-      const int c4 = (i & 31) * 4;
-      const int n = ctile * kTileN + c4;
-      if (n < p.N) {
+    // Every item of one thread has the same four columns (kThreads is a multiple of 32):
+    // their bias is fetched before the barrier, off the critical path.
+    const int c4 = (threadIdx.x & 31) * 4;
+    const int n = ctile * kTileN + c4;
+    float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (has_bias && n < p.N) {
+      const uint2 bb = __ldg(reinterpret_cast<const uint2*>(p.bias + n));
+      bias4[0] = bf16lo_f32(bb.x); bias4[1] = bf16hi_f32(bb.x);
+      bias4[2] = bf16lo_f32(bb.y); bias4[3] = bf16hi_f32(bb.y);
+    }
+    cluster_sync_all();
+    pdl_wait();
+    if (n < p.N) {
+      for (int i = threadIdx.x; i < (m_hi - m_lo) * 32; i += kThreads) {
+        const int j = i >> 5;
         const uint32_t a0 = recv0 + static_cast<uint32_t>(j * kTileN + c4) * 4u;
         float4 v[8];
 #pragma unroll
@@ -710,10 +625,9 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
         uint2 pk;
         if (has_bias) {
-          const uint2 bb = *reinterpret_cast<const uint2*>(p.bias + n);
           const uint32_t r01 = cvt_bf16x2(acc.y, acc.x), r23 = cvt_bf16x2(acc.w, acc.z);
-          pk.x = cvt_bf16x2(bf16hi_f32(r01) + bf16hi_f32(bb.x), bf16lo_f32(r01) + bf16lo_f32(bb.x));
-          pk.y = cvt_bf16x2(bf16hi_f32(r23) + bf16hi_f32(bb.y), bf16lo_f32(r23) + bf16lo_f32(bb.y));
+          pk.x = cvt_bf16x2(bf16hi_f32(r01) + bias4[1], bf16lo_f32(r01) + bias4[0]);
+          pk.y = cvt_bf16x2(bf16hi_f32(r23) + bias4[3], bf16lo_f32(r23) + bias4[2]);
         } else {
           pk.x = cvt_bf16x2(acc.y, acc.x);
           pk.y = cvt_bf16x2(acc.w, acc.z);
@@ -805,52 +719,8 @@ __global__ void wq_gemm_simt(const __nv_bfloat16* __restrict__ x, long long ldx,
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* f = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess)
-      f = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(f);
-  }();
-  return fn;
-}
-
-// rank-2 or rank-3 tiled map; dims/box innermost first, strides in bytes for dims 1..rank-1.
-static bool make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int rank,
-                     const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
-                     CUtensorMapSwizzle sw) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t d[3], st[2];
-  cuuint32_t bx[3], es[3] = {1, 1, 1};
-  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; bx[i] = box[i]; }
-  for (int i = 0; i + 1 < rank; ++i) st[i] = strides_bytes[i];
-  return fn(m, dt, rank, const_cast<void*>(base), d, st, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 static long long* g_trace = nullptr;
 
-struct DeviceInfo {
-  int sms = 0;
-  bool attr_set = false;
-};
-static DeviceInfo& device_info() {
-  static std::mutex mu;
-  static std::unordered_map<int, DeviceInfo> infos;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  std::lock_guard<std::mutex> lock(mu);
-  DeviceInfo& d = infos[dev];
-  if (d.sms == 0) cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
-  return d;
-}
 
 // Programmatic dependent launch is on unless DEXTER_B200_PDL=0.
 static bool pdl_enabled() {
@@ -862,31 +732,23 @@ static bool pdl_enabled() {
 }
 
 struct Plan {
-  int NU, planes, rows, units_per_tile, tiles, total_units, stages, w_stages, x_stage_bytes, ctas,
+  int NU, planes, rows, units_per_tile, tiles, tiles_n, total_units, stages, w_stages, x_stage_bytes, ctas,
       max_slots, nacc, recv_bytes, recv_off;
   size_t smem_bytes;
 };
 
-// Shapes the tensor-core kernel takes.  Everything else goes to wq_gemm_simt.
-static bool tc_supported(int M, int N, int K, int group, int bits) {
-  if (M < 1 || M > 128) return false;
-  if (N % 16 || N < 16) return false;
-  const int rows = bits == 4 ? K / 2 : K;
-  if (bits == 4 && (K % 2)) return false;
-  if (rows % kUnitRows) return false;
-  if (group % kUnitRows || K % group) return false;
-  if (K / group < 1) return false;
-  if ((N + kTileN - 1) / kTileN > kMaxTiles) return false;
-  return true;
-}
 
 static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   Plan pl{};
-  pl.NU = ((M + 15) / 16) * 16;
+  // More than 128 tokens: token blocks of 128, each (block, column tile) pair is a tile of
+  // its own, so one launch covers all of them and every SM stays busy.
+  const int blocks = (M + 127) / 128;
+  pl.NU = blocks > 1 ? 128 : ((M + 15) / 16) * 16;
   pl.planes = bits == 4 ? 2 : 1;
   pl.rows = bits == 4 ? K / 2 : K;
   pl.units_per_tile = pl.rows / kUnitRows;
-  pl.tiles = (N + kTileN - 1) / kTileN;
+  pl.tiles_n = (N + kTileN - 1) / kTileN;
+  pl.tiles = pl.tiles_n * blocks;
   pl.total_units = pl.units_per_tile * pl.tiles;
   pl.x_stage_bytes = pl.planes * pl.NU * 128;
   // Shared memory: four activation stages (one per unit slot, like the TMEM ring) and
@@ -897,7 +759,8 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   // Launches that may split tiles over a cluster keep room for its receive buffers
   // (at most NU + 8 token rows of 128 fp32) behind the two rings.
   const int budget_ctas = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
-  pl.recv_bytes = (pl.tiles * 2 <= budget_ctas && pl.units_per_tile >= 2) ? (pl.NU + 8) * kTileN * 4 : 0;
+  pl.recv_bytes = (blocks == 1 && pl.tiles * 2 <= budget_ctas && pl.units_per_tile >= 2)
+                      ? (pl.NU + 8) * kTileN * 4 : 0;
   int w_stages = (kSmemBudget - pl.recv_bytes - kAStages * pl.x_stage_bytes) / kWStage;
   if (pl.recv_bytes > 0 && w_stages < 2 * kAStages) {
     // not enough room for a useful weight ring next to the receive buffers: no cluster split
@@ -915,6 +778,17 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   // thread-block cluster instead, where it can), else `budget` CTAs, stream-K.
   const int budget = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
   int ctas = pl.tiles <= budget ? pl.tiles : budget;
+  if (pl.tiles > budget) {
+    // More tiles than CTAs.  Either every CTA takes `rounds` whole tiles (some SMs may idle
+    // in the last round, but nothing is split), or all CTAs take equal unit ranges and the
+    // tiles cut by a range boundary are reduced through global scratch, which costs about
+    // as much as 16 units.  Take whichever ends sooner.
+    const int rounds = (pl.tiles + budget - 1) / budget;
+    const int whole_ctas = (pl.tiles + rounds - 1) / rounds;
+    const long long whole_units = static_cast<long long>(rounds) * pl.units_per_tile;
+    const long long split_units = pl.total_units / budget + 16;
+    if (pl.tiles % whole_ctas == 0 && whole_units <= split_units) ctas = whole_ctas;
+  }
   if (ctas > pl.total_units) ctas = pl.total_units;
   pl.ctas = ctas;
   pl.nacc = 2;
@@ -929,10 +803,17 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   return pl;
 }
 
-constexpr size_t kStatusBytes = 256;
 // The counter block has one fixed size so that calls with different tile counts
 // never let one call's partial sums land on another call's counters.
 static size_t counters_bytes(int) { return static_cast<size_t>(kMaxTiles) * 4; }
+
+// Workspace the tensor-core launch of this problem needs (status, counters, partial sums).
+static size_t plan_workspace_bytes(int M, int N, int K, int bits, int max_ctas) {
+  DeviceInfo& di = device_info();
+  const Plan pl = make_plan(M, N, K, bits, di.sms > 0 ? di.sms : 148, max_ctas);
+  return kStatusBytes + counters_bytes(pl.tiles) +
+         static_cast<size_t>(pl.tiles) * pl.max_slots * pl.NU * kTileN * sizeof(float);
+}
 
 template <int BITS, bool HAS_ZERO>
 static int launch_tc(const void* x, long long ldx, const void* qw, const void* scales,
@@ -985,6 +866,7 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   p.NU = pl.NU;
   p.units_per_tile = pl.units_per_tile;
   p.tiles = pl.tiles;
+  p.tiles_n = pl.tiles_n;
   p.total_units = pl.total_units;
   p.half_k = BITS == 4 ? K / 2 : 0;
   p.stages = pl.stages;
@@ -1134,6 +1016,23 @@ int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const
                        (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 8 == 0) &&
                        (reinterpret_cast<uintptr_t>(out) % 8 == 0) && (ldo % 4 == 0) &&
                        (bits != 4 || (K / 2) % 8 == 0);
+  auto launch = [&](const char* xc, char* oc, int mc) -> int {
+    if (bits == 4)
+      return zeros ? launch_tc<4, true>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
+                                        group_size, workspace, workspace_bytes, max_ctas, stream)
+                   : launch_tc<4, false>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
+                                         group_size, workspace, workspace_bytes, max_ctas, stream);
+    return zeros ? launch_tc<8, true>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
+                                      group_size, workspace, workspace_bytes, max_ctas, stream)
+                 : launch_tc<8, false>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
+                                       group_size, workspace, workspace_bytes, max_ctas, stream);
+  };
+  // More than 128 tokens: one launch over all token blocks when the workspace holds the
+  // partial sums of that plan (dxb_workspace_bytes asks for it); a smaller workspace still
+  // works, block by block.
+  if (M > 128 && aligned && tc_supported(M, N, K, group_size, bits) &&
+      workspace_bytes >= plan_workspace_bytes(M, N, K, bits, max_ctas))
+    return launch(static_cast<const char*>(x), static_cast<char*>(out), M);
   // Token blocks of at most 128 rows per launch (the UMMA N of one accumulator); 96 when the
   // weight has so few tiles that the launch splits them over clusters, whose receive buffers
   // only fit next to the activation ring up to 96 tokens.
@@ -1144,16 +1043,7 @@ int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const
     const char* xc = static_cast<const char*>(x) + static_cast<long long>(m0) * ldx * 2;
     char* oc = static_cast<char*>(out) + static_cast<long long>(m0) * ldo * 2;
     if (aligned && tc_supported(mc, N, K, group_size, bits)) {
-      if (bits == 4)
-        rc = zeros ? launch_tc<4, true>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
-                                        group_size, workspace, workspace_bytes, max_ctas, stream)
-                   : launch_tc<4, false>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
-                                         group_size, workspace, workspace_bytes, max_ctas, stream);
-      else
-        rc = zeros ? launch_tc<8, true>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
-                                        group_size, workspace, workspace_bytes, max_ctas, stream)
-                   : launch_tc<8, false>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
-                                         group_size, workspace, workspace_bytes, max_ctas, stream);
+      rc = launch(xc, oc, mc);
     } else {
       rc = bits == 4 ? launch_simt<4>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
                                       group_size, stream)
@@ -1233,13 +1123,16 @@ int dxb_w8a16(const void* x, int64_t ldx, const void* qweight, const void* scale
 size_t dxb_workspace_bytes(int M, int N, int K, int bits) {
   using namespace dx;
   if (M <= 0 || N <= 0 || K <= 0 || (bits != 4 && bits != 8)) return kStatusBytes;
-  const int mc = M <= 128 ? M : 128;
   const int rows = bits == 4 ? K / 2 : K;
   if (rows < kUnitRows) return kStatusBytes;
-  DeviceInfo& di = device_info();
-  const Plan pl = make_plan(mc, N, K, bits, di.sms > 0 ? di.sms : 148, 0);
-  return kStatusBytes + counters_bytes(pl.tiles) +
-         static_cast<size_t>(pl.tiles) * pl.max_slots * pl.NU * kTileN * sizeof(float);
+  // Up to 128 tokens: that launch.  More: the larger of the one-launch plan over all token
+  // blocks and the plan of a single block (used when the caller's workspace is smaller).
+  const size_t one_block = plan_workspace_bytes(M <= 128 ? M : 128, N, K, bits, 0);
+  if (M <= 128) return one_block;
+  if (static_cast<long long>((N + kTileN - 1) / kTileN) * ((M + 127) / 128) > kMaxTiles)
+    return one_block;
+  const size_t all_blocks = plan_workspace_bytes(M, N, K, bits, 0);
+  return all_blocks > one_block ? all_blocks : one_block;
 }
 
 int dxb_dequantize(const void* qweight, const void* scales, const void* zeros, void* w_out, int N,

@@ -22,7 +22,7 @@ from .platform import ArchVersion, Capability
 from .registry import Priority, register, select
 
 __all__ = ["w4a16", "w8a16", "linear", "dequantize", "accepts", "KERNEL_NAMES", "register_with",
-           "last_status"]
+           "last_status", "chain", "chain_status", "ChainLink", "CHAIN_MAX"]
 
 KERNEL_NAMES = {"w4a16": "b200_w4a16_tcgen05", "w8a16": "b200_w8a16_tcgen05"}
 
@@ -136,6 +136,112 @@ def w4a16(x, qweight, scales, zeros, bias, group_size, *, max_ctas: int = 0):
 def w8a16(x, qweight, scales, zeros, bias, group_size, *, max_ctas: int = 0):
     """int8 weight-only GEMM, bf16 in / bf16 out (``max_ctas``: see :func:`w4a16`)."""
     return _run(8, x, qweight, scales, zeros, bias, group_size, max_ctas)
+
+
+CHAIN_MAX = _lib.DXB_CHAIN_MAX
+
+
+class ChainLink:
+    """One GEMM of a :func:`chain`: the kernel-slot arguments plus where ``x`` comes from.
+
+    ``x`` is either a tensor that is ready before the call, or the integer index of an
+    EARLIER link whose output is this link's activations.
+    """
+
+    __slots__ = ("x", "qweight", "scales", "zeros", "bias", "group_size")
+
+    def __init__(self, x, qweight, scales, zeros=None, bias=None, group_size=128):
+        self.x, self.qweight, self.scales = x, qweight, scales
+        self.zeros, self.bias, self.group_size = zeros, bias, group_size
+
+
+# One chain workspace per (device, stream): zero-filled when created; the kernel leaves it clean.
+_chain_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def chain(links, *, bits: int = 4, max_ctas: int = 0):
+    """Run a list of quantised GEMMs (at most ``CHAIN_MAX``) as ONE launch.
+
+    Each link computes what ``w4a16`` / ``w8a16`` would; links are started in list order
+    by one persistent grid, and a link whose ``x`` is an index waits in the kernel for
+    that link's output instead of for a kernel boundary.  Returns the list of outputs.
+    All links need at most 128 token rows and shapes the tensor-core kernel takes;
+    otherwise the library refuses (``RuntimeError``) and the caller should issue the
+    GEMMs one by one.
+    """
+    if bits not in (4, 8):
+        raise ValueError(f"weight-only quantisation supports 4 or 8 bits, got {bits}")
+    links = list(links)
+    if not 1 <= len(links) <= CHAIN_MAX:
+        raise ValueError(f"a chain holds 1..{CHAIN_MAX} GEMMs, got {len(links)}")
+    items = (_lib.ChainItem * len(links))()
+    outs, keep = [], []
+    device = links[0].qweight.device
+    if device.type != "cuda":
+        raise RuntimeError("the B200 backend needs CUDA tensors; there is no CPU path")
+    for i, ln in enumerate(links):
+        k_dim = ln.qweight.shape[0] * (2 if bits == 4 else 1)
+        n = ln.qweight.shape[1]
+        if isinstance(ln.x, int):
+            if not 0 <= ln.x < i:
+                raise ValueError(f"link {i} depends on link {ln.x}, which does not come before it")
+            x2, dep = outs[ln.x], ln.x
+        else:
+            x2, dep = ln.x.reshape(-1, ln.x.shape[-1]), -1
+            if x2.dtype != torch.bfloat16:
+                raise RuntimeError("the B200 backend computes bf16 activations only")
+            if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
+                x2 = x2.contiguous()
+        if x2.shape[1] != k_dim:
+            raise ValueError(f"link {i}: x has K={x2.shape[1]} but the packed weight has K={k_dim}")
+        if ln.qweight.dtype != torch.uint8 or ln.scales.dtype != torch.bfloat16:
+            raise ValueError("packed weights must be uint8 with bf16 scales")
+        qweight, scales = ln.qweight.contiguous(), ln.scales.contiguous()
+        zeros = None if ln.zeros is None else ln.zeros.contiguous()
+        bias = None if ln.bias is None else ln.bias.contiguous()
+        m = x2.shape[0]
+        out = torch.empty((m, n), device=device, dtype=torch.bfloat16)
+        keep.append((x2, qweight, scales, zeros, bias))
+        outs.append(out)
+        it = items[i]
+        it.x, it.ldx = x2.data_ptr(), x2.stride(0)
+        it.qweight, it.scales = qweight.data_ptr(), scales.data_ptr()
+        it.zeros, it.bias = _ptr(zeros), _ptr(bias)
+        it.out, it.ldo = out.data_ptr(), n
+        it.M, it.N, it.K, it.group_size = m, n, k_dim, ln.group_size
+        it.depends_on = dep
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream().cuda_stream
+        need = _LIB.dxb_chain_workspace_bytes(bits, items, len(links), max_ctas)
+        if need == 0:
+            # let the launch call report why
+            need = 256
+        key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+        ws = _chain_workspaces.get(key)
+        if ws is None or ws.numel() < need:
+            ws = torch.zeros(max(need, 256), dtype=torch.uint8, device=device)
+            _chain_workspaces[key] = ws
+        rc = _LIB.dxb_wq_gemm_chain(bits, items, len(links), ws.data_ptr(), ws.numel(), max_ctas,
+                                    ctypes.c_void_p(stream))
+        if rc != _lib.OK:
+            _raise(rc)
+        if os.environ.get("DEXTER_B200_CHECK"):
+            code = _LIB.dxb_read_status(ws.data_ptr(), ctypes.c_void_p(stream))
+            if code != _lib.OK:
+                ws.zero_()
+                _raise(code)
+    return outs
+
+
+def chain_status(device: Optional[torch.device] = None) -> int:
+    """Synchronise and return the status word of the current stream's chain workspace."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream().cuda_stream
+        ws = _chain_workspaces.get((device.index, stream))
+        if ws is None:
+            return _lib.OK
+        return _LIB.dxb_read_status(ws.data_ptr(), ctypes.c_void_p(stream))
 
 
 def dequantize(qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor],

@@ -97,6 +97,60 @@ int dxb_wq_gemm_static(int bits, const void* x, int64_t ldx, const void* qweight
                        const void* scales, const void* zeros, const void* bias, void* out,
                        int64_t ldo, int M, int N, int K, int group_size, void* cuda_stream);
 
+/*
+ * Several GEMMs of one layer in ONE launch.  The reference runs a block's linears as
+ * successive calls of the kernel slot, one launch each (ops.linear,
+ * python/dexter/ops/__init__.py:89-112, called per projection from
+ * python/dexter/models/layers.py:44-50); at
+ * M <= 128 tokens each of those launches is dominated by its start-up and drain.  A
+ * chain hands the whole list to one persistent grid (one CTA per SM): every CTA works
+ * through the items in order, the packed-weight pipeline of item i+1 fills while item
+ * i drains, and an item whose activations are an earlier item's output waits on a
+ * completion count in global memory instead of a kernel boundary.
+ *
+ * Rules:
+ *   - 1 <= n_items <= DXB_CHAIN_MAX; every item must be a shape the tensor-core kernel
+ *     takes (dxb_uses_tensor_cores, M <= 128, 16-byte aligned pointers and strides) with
+ *     at least 8 units of 128 (int4) or 64 (int8) rows of K; all items share `bits` and
+ *     either all or none have zero points; otherwise DXB_ERR_UNSUPPORTED and nothing is
+ *     launched (call dxb_wq_gemm per item instead).
+ *   - depends_on = index of the EARLIER item whose `out` buffer this item's `x` reads,
+ *     or -1 when `x` is ready before the call.  An item may depend on one item only.
+ *     Items are started in list order; placing an independent item between a producer
+ *     and its consumer hides the hand-over completely.
+ *   - no `out` buffer may overlap another item's `out` or any item's `x` other than
+ *     that of the items that name it in depends_on.
+ *   - `workspace`: at least dxb_chain_workspace_bytes() (a status word and completion
+ *     counts; partial sums stay in shared memory), 256-byte aligned, zero-filled once
+ *     before its first use; the kernel leaves it clean after every normal completion.
+ *     Calls that may overlap on the GPU need different workspaces.
+ *   - the grid (clusters of 2, 4 or 8 CTAs, as many as are resident at once) is sized for
+ *     a GPU that this stream has to itself while the chain runs.  Every in-kernel wait is
+ *     bounded: if part of the grid cannot become resident because other work holds SMs,
+ *     the call ends with DXB_ERR_KERNEL_TIMEOUT in dxb_read_status(workspace), it does
+ *     not hang.
+ * Each item computes what dxb_wq_gemm computes for it (same dequantisation, fp32
+ * accumulation, bf16 rounding, bias order); only the split of the K range differs, and the
+ * partial sums of a tile are always added in the same order, so runs are reproducible.
+ */
+#define DXB_CHAIN_MAX 32
+typedef struct dxb_chain_item {
+  const void* x;
+  int64_t ldx;
+  const void* qweight;
+  const void* scales;
+  const void* zeros;
+  const void* bias;
+  void* out;
+  int64_t ldo;
+  int M, N, K, group_size;
+  int depends_on;
+} dxb_chain_item;
+
+size_t dxb_chain_workspace_bytes(int bits, const dxb_chain_item* items, int n_items, int max_ctas);
+int dxb_wq_gemm_chain(int bits, const dxb_chain_item* items, int n_items, void* workspace,
+                      size_t workspace_bytes, int max_ctas, void* cuda_stream);
+
 /* Bytes of workspace dxb_wq_gemm needs for this problem on the current device. */
 size_t dxb_workspace_bytes(int M, int N, int K, int bits);
 
