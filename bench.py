@@ -180,21 +180,21 @@ def time_graph(graph, iters: int):
     return e0.elapsed_time(e1)
 
 
-def single_gemm_figures(d, ops, peaks) -> dict:
-    """The headline GEMM alone: M=83, K=3072, N=14336, int4 g128, 16 rotating weights."""
+def gemm_figures(d, ops, peaks, m, k, n, bits=4, group=128, rotate=16, reps=7) -> dict:
+    """One GEMM shape alone, over `rotate` weight buffers so that weights come from HBM."""
     import torch
 
-    m, k, n = M_TOKENS, 3072, 14336
     torch.manual_seed(0)
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
-    base = d.quantize((torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16), bits=4,
-                      group_size=128, symmetric=True)
+    base = d.quantize((torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16), bits=bits,
+                      group_size=group, symmetric=True)
     weights = [(torch.randint(0, 256, base.qweight.shape, dtype=torch.uint8, device="cuda"),
-                base.scales.clone()) for _ in range(16)]
+                base.scales.clone()) for _ in range(rotate)]
+    fn = ops.w4a16 if bits == 4 else ops.w8a16
 
     def body():
         for q, s in weights:
-            ops.w4a16(x, q, s, None, None, 128)
+            fn(x, q, s, None, None, group)
 
     body()
     torch.cuda.synchronize()
@@ -203,14 +203,59 @@ def single_gemm_figures(d, ops, peaks) -> dict:
         body()
     graph.replay()
     torch.cuda.synchronize()
-    best = min(time_graph(graph, 4) for _ in range(7)) * 1e3 / (4 * len(weights))  # us per GEMM
+    best = min(time_graph(graph, 4) for _ in range(reps)) * 1e3 / (4 * len(weights))  # us per GEMM
     wbytes = base.nbytes
     flops = 2.0 * m * k * n
     t_mem = wbytes / (peaks["hbm_gbs"] * 1e3)      # us
     t_mma = flops / (peaks["tflops"] * 1e6)        # us
-    return {"shape": [m, k, n], "us": best, "tflops": flops / best * 1e-6, "gbs": wbytes / best * 1e-3,
-            "frac_hbm": t_mem / best, "frac_tensor": t_mma / best, "frac_roofline": max(t_mem, t_mma) / best,
-            "roofline_us": max(t_mem, t_mma), "launches_timed": 7 * 4 * len(weights)}
+    return {"shape": [m, k, n], "bits": bits, "group": group, "us": best, "tflops": flops / best * 1e-6,
+            "gbs": wbytes / best * 1e-3, "frac_hbm": t_mem / best, "frac_tensor": t_mma / best,
+            "frac_roofline": max(t_mem, t_mma) / best, "roofline_us": max(t_mem, t_mma),
+            "bound": "hbm" if t_mem >= t_mma else "tensor", "launches_timed": reps * 4 * len(weights)}
+
+
+def single_gemm_figures(d, ops, peaks) -> dict:
+    """The headline GEMM alone: M=83, K=3072, N=14336, int4 g128, 16 rotating weights."""
+    return gemm_figures(d, ops, peaks, M_TOKENS, 3072, 14336, 4, 128, rotate=16)
+
+
+SWEEP_SHAPES = (("qkv", 3072, 9216), ("o", 3072, 3072), ("up", 3072, 14336), ("down", 14336, 3072))
+SWEEP_M = (1, 8, 32, 83, 256, 512, 913)
+
+
+def run_gemm_only(args) -> int:
+    """``--gemm M,K,N[,bits[,group]]``: time that one shape on cuda:0 and print one JSON line.
+    ``--gemm sweep``: the M sweep over the 5B linear shapes, int4 group 128 and int8 per
+    channel, one JSON line per shape."""
+    import torch
+
+    torch.cuda.set_device(0)
+    import dexter_labs_b200 as d
+    from dexter_labs_b200 import ops
+
+    peaks = load_peaks()
+
+    def one(m, k, n, bits, group, reps, name=None):
+        wbytes = (k * n // 2 if bits == 4 else k * n)
+        rotate = max(2, min(16, int(400e6 // max(wbytes, 1)) + 1))  # > 126 MB L2 where memory allows
+        fig = gemm_figures(d, ops, peaks, m, k, n, bits, group, rotate=rotate, reps=reps)
+        fig.update({"metric": "wq_gemm_us", "rotating_weights": rotate, "peak_source": peaks["source"]})
+        if name:
+            fig["name"] = name
+        print(json.dumps(fig), flush=True)
+
+    if args.gemm == "sweep":
+        for name, k, n in SWEEP_SHAPES:
+            for bits in (4, 8):
+                for m in SWEEP_M:
+                    one(m, k, n, bits, 128 if bits == 4 else k, min(args.reps, 3), name)
+        return 0
+    parts = [int(v) for v in args.gemm.split(",")]
+    m, k, n = parts[:3]
+    bits = parts[3] if len(parts) > 3 else 4
+    group = parts[4] if len(parts) > 4 else (128 if bits == 4 else k)
+    one(m, k, n, bits, group, args.reps)
+    return 0
 
 
 def finish(world: int, code: int) -> None:
@@ -448,7 +493,13 @@ def main() -> int:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--collective", choices=("all_reduce", "rs_ag"), default="all_reduce",
                     help="how row-parallel partial sums are combined when N > 1")
+    ap.add_argument("--gemm", default=None, metavar="M,K,N[,bits[,group]] | sweep",
+                    help="time this one GEMM shape only (1 GPU) instead of the layer set; "
+                         "`sweep` = M in {1..913} over the 5B linear shapes, int4 and int8")
+    ap.add_argument("--reps", type=int, default=7, help="timed repetitions of --gemm (best is kept)")
     args = ap.parse_args()
+    if args.gemm and args.impl == "ours":
+        return run_gemm_only(args)
     return run_reference(args) if args.impl == "reference" else run_ours(args)
 
 

@@ -69,7 +69,9 @@ struct WqParams {
 };
 
 
-template <int BITS, bool HAS_ZERO>
+// MULTI: more than one token block (M > 128); a tile is then a (token block, column tile)
+// pair.  The single-block kernel carries none of that bookkeeping.
+template <int BITS, bool HAS_ZERO, bool MULTI>
 __global__ void __launch_bounds__(kThreads, 1)
 wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_x,
            const WqParams p) {
@@ -142,7 +144,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const int pi = warp == 0 ? 0 : 1;
       int tile = tile_begin, ku = ku_begin + pi, s = pi;
       while (ku >= U) { ku -= U; ++tile; }
-      int ntile = tile % p.tiles_n;
+      int ntile = MULTI ? tile % p.tiles_n : 0;
       uint32_t ph = 0;
       int issued = 0;
       bool ok = true;
@@ -152,14 +154,14 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (elect_one()) {
           const uint32_t fw = bar0 + 8 * (kBarFullW + s);
           mbar_expect_tx(fw, kQBytes);
-          tma_load_2d(w_ring + s * kWStage, &tm_q, fw, ntile * kTileN, ku * kUnitRows);
+          tma_load_2d(w_ring + s * kWStage, &tm_q, fw, (MULTI ? ntile : tile) * kTileN, ku * kUnitRows);
         }
         __syncwarp();
         ++issued;
         s += 2;
         if (s >= SW) { s -= SW; ph ^= 1u; }
         ku += 2;
-        while (ku >= U) { ku -= U; ++tile; if (++ntile == p.tiles_n) ntile = 0; }
+        while (ku >= U) { ku -= U; ++tile; if (MULTI && ++ntile == p.tiles_n) ntile = 0; }
       }
       if (!ok && lane == 0) {
         // Leaving early: let the copies already issued land before the CTA exits.
@@ -174,8 +176,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     pdl_wait();
     {
       int ku = ku_begin, t = 0;
-      int ntile = tile_begin % p.tiles_n;
-      int row0 = (tile_begin / p.tiles_n) * 128;  // first token row of the tile's token block
+      int ntile = MULTI ? tile_begin % p.tiles_n : 0;
+      int row0 = MULTI ? (tile_begin / p.tiles_n) * 128 : 0;  // first token row of the token block
       uint32_t ph = 0;
       int issued = 0;
       bool ok = true;
@@ -196,7 +198,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (++t == kAStages) { t = 0; ph ^= 1u; }
         if (++ku == U) {
           ku = 0;
-          if (++ntile == p.tiles_n) { ntile = 0; row0 += 128; }
+          if (MULTI && ++ntile == p.tiles_n) { ntile = 0; row0 += 128; }
         }
       }
       if (!ok && lane == 0) {
@@ -280,10 +282,11 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const int left = u_end - u;
       const int nun = left < (U - ku0) ? left : (U - ku0);
       const bool whole = (nun == U);
-      const int tblock = tile / p.tiles_n;           // token block of this tile
-      const int ntile = tile - tblock * p.tiles_n;   // its 128 weight columns
+      const int tblock = MULTI ? tile / p.tiles_n : 0;  // token block of this tile
+      const int ntile = tile - tblock * p.tiles_n;      // its 128 weight columns
       const int row0 = tblock * 128;
-      const int m_rows = (p.M - row0) < 128 ? (p.M - row0) : 128;  // token rows in this block
+      // token rows in this block
+      const int m_rows = MULTI ? ((p.M - row0) < 128 ? (p.M - row0) : 128) : p.M;
       const int n = ntile * kTileN + n_local;
       const bool n_ok = n < p.N;
       // The bias does not depend on the accumulator: fetch it before waiting, so that its
@@ -476,6 +479,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     int u = u_begin + team;
     int tile = tile_begin, ku = ku_begin + team;
     while (ku >= U) { ku -= U; ++tile; }
+    int ntile = MULTI ? tile % p.tiles_n : 0;  // column tile of `tile`, kept in step without divisions
     int s = team;  // SW is a multiple of the team count: stages j, j+4, ... belong to team j
     uint32_t ph = 0;
     uint32_t aph = 0;
@@ -484,8 +488,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // L2), fetched one team-unit ahead so the load latency is never waited for.
     uint2 sc[PLANES], zr[PLANES], sc_nx[PLANES], zr_nx[PLANES];
     const int n4_stride = p.N >> 2;  // uint2 (4 x bf16) elements per scale row
-    auto load_sz = [&](int tile_, int ku_, uint2 (&s_out)[PLANES], uint2 (&z_out)[PLANES]) {
-      const int n = (tile_ % p.tiles_n) * kTileN + n_local;
+    auto load_sz = [&](int tile_, int ntile_, int ku_, uint2 (&s_out)[PLANES], uint2 (&z_out)[PLANES]) {
+      const int n = ntile_ * kTileN + n_local;
       const bool in = n < p.N && tile_ < p.tiles;
 #pragma unroll
       for (int pl = 0; pl < PLANES; ++pl) {
@@ -496,14 +500,15 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (HAS_ZERO) z_out[pl] = in ? __ldg(zr_ptr + idx) : make_uint2(0u, 0u);
       }
     };
-    if (u < u_end) load_sz(tile, ku, sc_nx, zr_nx);
+    if (u < u_end) load_sz(tile, MULTI ? ntile : tile, ku, sc_nx, zr_nx);
     for (; u < u_end; u += kAStages) {
 #pragma unroll
       for (int pl = 0; pl < PLANES; ++pl) { sc[pl] = sc_nx[pl]; if (HAS_ZERO) zr[pl] = zr_nx[pl]; }
       {
         int ku_n = ku + kAStages, tile_n = tile;
-        while (ku_n >= U) { ku_n -= U; ++tile_n; }
-        if (u + kAStages < u_end) load_sz(tile_n, ku_n, sc_nx, zr_nx);
+        int ntile_n = ntile;
+        while (ku_n >= U) { ku_n -= U; ++tile_n; if (MULTI && ++ntile_n == p.tiles_n) ntile_n = 0; }
+        if (u + kAStages < u_end) load_sz(tile_n, MULTI ? ntile_n : tile_n, ku_n, sc_nx, zr_nx);
       }
       ok = mbar_wait(bar0 + 8 * (kBarFullW + s), ph, abortp);
       if (!ok) break;
@@ -583,7 +588,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       s += kAStages;
       if (s >= SW) { s -= SW; ph ^= 1u; }
       ku += kAStages;
-      while (ku >= U) { ku -= U; ++tile; }
+      while (ku >= U) { ku -= U; ++tile; if (MULTI && ++ntile == p.tiles_n) ntile = 0; }
     }
   }
 
@@ -882,12 +887,14 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   }
   p.trace = g_trace;
 
-  auto kernel = wq_gemm_tc<BITS, HAS_ZERO>;
+  auto kernel = pl.tiles > pl.tiles_n ? wq_gemm_tc<BITS, HAS_ZERO, true> : wq_gemm_tc<BITS, HAS_ZERO, false>;
   static thread_local int attr_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (attr_dev != dev) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(wq_gemm_tc<BITS, HAS_ZERO, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemBudget + 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(wq_gemm_tc<BITS, HAS_ZERO, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemBudget + 1024) != cudaSuccess)
       return DXB_ERR_CUDA;
     attr_dev = dev;
@@ -1093,7 +1100,14 @@ int dxb_wq_gemm_static(int bits, const void* x, int64_t ldx, const void* qweight
   int rc = check_args(bits, x, ldx, qweight, scales, out, ldo, M, N, K, group_size);
   if (rc != DXB_OK) return rc;
   if (M == 0) return DXB_OK;
-  if (dxb_workspace_bytes(M, N, K, bits) > kStaticScratchBytes) return DXB_ERR_SCRATCH_LIMIT;
+  // What one launch of at most 128 tokens needs; with more tokens dxb_wq_gemm takes the
+  // one-launch plan when the array holds it and goes block by block otherwise.
+  {
+    const int rows = bits == 4 ? K / 2 : K;
+    if (rows >= kUnitRows &&
+        plan_workspace_bytes(M <= 128 ? M : 128, N, K, bits, 0) > kStaticScratchBytes)
+      return DXB_ERR_SCRATCH_LIMIT;
+  }
   void* scratch = nullptr;
   rc = static_scratch_address(&scratch);
   if (rc != DXB_OK) return rc;

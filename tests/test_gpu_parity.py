@@ -305,3 +305,40 @@ def test_two_streams_do_not_share_scratch(d, oracle):
     torch.cuda.synchronize()
     for o in outs:
         assert torch.equal(o.view(torch.int16), want.view(torch.int16))
+
+
+# ------------------------------------------------ more than 128 tokens, both plans
+@pytest.mark.parametrize("m,k,n,nbits", [(300, 1024, 2048, 4), (913, 3072, 3072, 4), (257, 2048, 1040, 8)])
+def test_large_m_one_launch_and_block_by_block_agree(m, k, n, nbits, d, oracle, b200_lib):
+    """M > 128: one launch over all token blocks when the workspace holds that plan's partial
+    sums, block-by-block launches through a workspace sized for 128 tokens otherwise.  Both are
+    checked against the oracle and against each other."""
+    import ctypes
+
+    x, qw, bias = seeded(d, m, k, n, nbits, 128 if nbits == 4 else k, True, 5, bias=True)
+    x, bias = x.cuda(), bias.cuda()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call(nbytes):
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        rc = b200_lib.dxb_wq_gemm(nbits, ctypes.c_void_p(x.data_ptr()), k,
+                                  ctypes.c_void_p(qw.qweight.data_ptr()),
+                                  ctypes.c_void_p(qw.scales.data_ptr()), None,
+                                  ctypes.c_void_p(bias.data_ptr()), ctypes.c_void_p(out.data_ptr()), n,
+                                  m, n, k, qw.group_size, ctypes.c_void_p(ws.data_ptr()), nbytes, 0,
+                                  stream)
+        assert rc == 0, b200_lib.dxb_strerror(rc)
+        assert b200_lib.dxb_read_status(ctypes.c_void_p(ws.data_ptr()), stream) == 0
+        return out
+
+    full = b200_lib.dxb_workspace_bytes(m, n, k, nbits)
+    one_block = b200_lib.dxb_workspace_bytes(128, n, k, nbits)
+    assert full >= one_block
+    y_one_launch = call(full)
+    y_blocks = call(one_block)
+    want = oracle.torch_wq_gemm(x.cpu(), qw.qweight.cpu(), qw.scales.cpu(), None, bias.cpu(),
+                                qw.group_size, nbits).float()
+    assert err(y_one_launch.cpu().float(), want) < TOL
+    assert err(y_blocks.cpu().float(), want) < TOL
+    assert err(y_one_launch.cpu().float(), y_blocks.cpu().float()) < TOL
