@@ -249,6 +249,9 @@ def run_gemm_only(args) -> int:
             for bits in (4, 8):
                 for m in SWEEP_M:
                     one(m, k, n, bits, 128 if bits == 4 else k, min(args.reps, 3), name)
+        # the 14B-shaped linears (dim 5120, FFN 13824) at the compute-bound token count
+        for name, k, n in (("14b_qkvo", 5120, 5120), ("14b_up", 5120, 13824), ("14b_down", 13824, 5120)):
+            one(913, k, n, 4, 128, min(args.reps, 3), name)
         return 0
     parts = [int(v) for v in args.gemm.split(",")]
     m, k, n = parts[:3]

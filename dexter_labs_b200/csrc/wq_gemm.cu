@@ -778,22 +778,21 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   pl.recv_off = pl.w_stages * kWStage + pl.stages * pl.x_stage_bytes;
   pl.smem_bytes = static_cast<size_t>(pl.recv_off) + pl.recv_bytes + 1024;
   // Grid: `budget` CTAs at most (all SMs unless the caller caps it, e.g. to run several
-  // GEMMs side by side).  One CTA per tile when the tiles fit the budget (splitting them
-  // through global scratch costs more than it gains; the launcher splits tiles across a
-  // thread-block cluster instead, where it can), else `budget` CTAs, stream-K.
+  // GEMMs side by side).
   const int budget = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
-  int ctas = pl.tiles <= budget ? pl.tiles : budget;
-  if (pl.tiles > budget) {
-    // More tiles than CTAs.  Either every CTA takes `rounds` whole tiles (some SMs may idle
-    // in the last round, but nothing is split), or all CTAs take equal unit ranges and the
-    // tiles cut by a range boundary are reduced through global scratch, which costs about
-    // as much as 16 units.  Take whichever ends sooner.
-    const int rounds = (pl.tiles + budget - 1) / budget;
-    const int whole_ctas = (pl.tiles + rounds - 1) / rounds;
-    const long long whole_units = static_cast<long long>(rounds) * pl.units_per_tile;
-    const long long split_units = pl.total_units / budget + 16;
-    if (pl.tiles % whole_ctas == 0 && whole_units <= split_units) ctas = whole_ctas;
-  }
+  // Two ways to hand out the work.  Whole tiles: every CTA takes `rounds` complete tiles
+  // (CTAs may idle, nothing is split).  Equal unit ranges over all CTAs (stream-K): nobody
+  // idles, but the tiles cut by a range boundary go through global scratch, which costs
+  // as much as a few dozen units.  Take whichever ends sooner.  (Few tiles in one token block
+  // are split over clusters instead; the launcher decides that, see launch_tc.)
+  const int rounds = (pl.tiles + budget - 1) / budget;
+  const int whole_ctas = (pl.tiles + rounds - 1) / rounds;
+  const long long whole_units = static_cast<long long>(rounds) * pl.units_per_tile;
+  // measured cost of the global fix-up in units: ~16 at <= 96 tokens, ~28 with 128-token
+  // accumulators (larger partial tiles); half as much again for int8, whose units are shorter
+  const int fixup_units = (pl.NU > 96 ? 28 : 16) * (bits == 8 ? 3 : 2) / 2;
+  const long long split_units = (pl.total_units + budget - 1) / budget + fixup_units;
+  int ctas = (pl.tiles % whole_ctas == 0 && whole_units <= split_units) ? whole_ctas : budget;
   if (ctas > pl.total_units) ctas = pl.total_units;
   pl.ctas = ctas;
   pl.nacc = 2;
