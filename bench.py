@@ -219,6 +219,60 @@ def single_gemm_figures(d, ops, peaks) -> dict:
     return gemm_figures(d, ops, peaks, M_TOKENS, 3072, 14336, 4, 128, rotate=16)
 
 
+def chain_figures(d, ops) -> dict:
+    """The ten linears of one 5B block as ONE launch (ops.chain) against ten launches.
+
+    Order of the links: cross v, self q/k/v, cross k (all read the block input or the
+    context), then cross o (reads cross v), self o (reads self v), cross q (reads self o),
+    FFN up (reads cross o), FFN down (reads up): every consumer has at least one
+    independent link between it and its producer, except up -> down.
+    """
+    import torch
+
+    torch.manual_seed(0)
+    dim, ffn, m = 3072, 14336, M_TOKENS
+    x = torch.randn(m, dim, device="cuda").to(torch.bfloat16)
+    ctx = torch.randn(m, dim, device="cuda").to(torch.bfloat16)
+    spec = [(ctx, dim, dim), (x, dim, dim), (x, dim, dim), (x, dim, dim), (ctx, dim, dim),
+            (0, dim, dim), (3, dim, dim), (6, dim, dim), (5, dim, ffn), (8, ffn, dim)]
+    links = []
+    for src, k, n in spec:
+        qw = d.quantize((torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16), bits=4,
+                        group_size=128, symmetric=True)
+        bias = (torch.randn(n, device="cuda") * 0.1).to(torch.bfloat16)
+        links.append(ops.ChainLink(src, qw.qweight, qw.scales, None, bias, 128))
+
+    def as_chain():
+        return ops.chain(links, bits=4)
+
+    def as_launches():
+        outs = []
+        for ln in links:
+            xin = outs[ln.x] if isinstance(ln.x, int) else ln.x
+            outs.append(ops.w4a16(xin, ln.qweight, ln.scales, None, ln.bias, 128))
+        return outs
+
+    def time_us(fn, per=4):
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(per):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        return min(time_graph(graph, 10) for _ in range(5)) * 1e3 / (10 * per)
+
+    a, b = as_chain(), as_launches()
+    torch.cuda.synchronize()
+    diff = max(float((p.float() - q.float()).abs().max() / q.float().abs().max().clamp_min(1e-6))
+               for p, q in zip(a, b))
+    return {"metric": "w4a16_5b_block_us", "links": len(links), "tokens": m,
+            "one_launch_us": time_us(as_chain), "ten_launches_us": time_us(as_launches),
+            "max_normalised_diff": diff, "chain_status": ops.chain_status(),
+            "note": "weights of one block (84 MB) stay in the 126 MB L2 across replays in both arms"}
+
+
 SWEEP_SHAPES = (("qkv", 3072, 9216), ("o", 3072, 3072), ("up", 3072, 14336), ("down", 14336, 3072))
 SWEEP_M = (1, 8, 32, 83, 256, 512, 913)
 
@@ -226,7 +280,8 @@ SWEEP_M = (1, 8, 32, 83, 256, 512, 913)
 def run_gemm_only(args) -> int:
     """``--gemm M,K,N[,bits[,group]]``: time that one shape on cuda:0 and print one JSON line.
     ``--gemm sweep``: the M sweep over the 5B linear shapes, int4 group 128 and int8 per
-    channel, one JSON line per shape."""
+    channel, one JSON line per shape.  ``--gemm chain``: one 5B block as one chained launch
+    against ten launches."""
     import torch
 
     torch.cuda.set_device(0)
@@ -244,6 +299,9 @@ def run_gemm_only(args) -> int:
             fig["name"] = name
         print(json.dumps(fig), flush=True)
 
+    if args.gemm == "chain":
+        print(json.dumps(chain_figures(d, ops)), flush=True)
+        return 0
     if args.gemm == "sweep":
         for name, k, n in SWEEP_SHAPES:
             for bits in (4, 8):
@@ -496,7 +554,7 @@ def main() -> int:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--collective", choices=("all_reduce", "rs_ag"), default="all_reduce",
                     help="how row-parallel partial sums are combined when N > 1")
-    ap.add_argument("--gemm", default=None, metavar="M,K,N[,bits[,group]] | sweep",
+    ap.add_argument("--gemm", default=None, metavar="M,K,N[,bits[,group]] | sweep | chain",
                     help="time this one GEMM shape only (1 GPU) instead of the layer set; "
                          "`sweep` = M in {1..913} over the 5B linear shapes, int4 and int8")
     ap.add_argument("--reps", type=int, default=7, help="timed repetitions of --gemm (best is kept)")

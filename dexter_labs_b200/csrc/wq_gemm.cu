@@ -11,22 +11,27 @@
 //
 // Tensor-core kernel (wq_gemm_tc): the weight tile is the 128-row UMMA "M"
 // operand and the tokens are the UMMA "N" (swap-AB), so M = 83 tokens costs a
-// 96-wide MMA instead of a 128-row one.  Per CTA, per unit of 64 packed rows x
-// 128 columns:
-//   warp 0      TMA producer: packed bytes (+ scale / zero rows) and the matching
-//               X k-slices land in a shared-memory ring (128 B swizzle).
-//   warps 6-13  dequantise: ld.shared of packed words, nibble -> bf16 by bit
-//               pattern (OR into 0x4300 = 128.0, exact subtract, one multiply; no
-//               int->float convert), k-pairs formed with two byte permutes, and
-//               written straight into TMEM with tcgen05.st.16x128b (the dequantised
-//               tile never touches shared memory).
-//   warp 1      one thread issues tcgen05.mma (A = weights from TMEM, B = X from
-//               shared memory, fp32 accumulators in TMEM).
-//   warps 2-5   epilogue: tcgen05.ld, bias, bf16 stores; or fp32 partials.
-// Work is split stream-K style: the (tile, unit) space is cut into equal contiguous
-// ranges, one per CTA; a tile shared by several CTAs is finished by whichever CTA
-// arrives last (no CTA ever waits for another one), summing the partials in a
-// fixed order so results are deterministic.
+// 96-wide MMA instead of a 128-row one.  24 warps per CTA, one CTA per SM; per unit
+// of 64 packed rows x 128 columns:
+//   warps 0, 3   TMA producers: packed bytes of alternate units land in a
+//                shared-memory ring (128 B swizzle).
+//   warp 2       TMA producer: the matching activation k-slices (both nibble planes
+//                in one 3-D box for int4).
+//   warps 8-23   four dequant teams of four warps, one unit each in flight:
+//                ld.shared of packed words, nibble -> bf16 by bit pattern (OR into
+//                0x4300 = 128.0, exact subtract, one multiply; no int->float convert),
+//                k-pairs formed with two byte permutes, written straight into TMEM with
+//                tcgen05.st.16x128b (the dequantised tile never touches shared memory);
+//                scales and zero points come from global memory one unit ahead.
+//   warp 1       one lane issues tcgen05.mma (A = weights from TMEM, B = activations
+//                from shared memory, fp32 accumulators in TMEM, two accumulators).
+//   warps 4-7    epilogue: tcgen05.ld, bias, bf16 stores; or fp32 partial sums.
+// How the (tile, unit) space is handed to CTAs is chosen per launch (make_plan,
+// launch_tc): whole tiles per CTA; equal contiguous unit ranges (stream-K), where a tile
+// shared by several CTAs is finished by whichever CTA arrives last (no CTA ever waits for
+// another one), summing the partials in a fixed order; or, for few tiles, one
+// thread-block cluster per tile that splits K and adds through distributed shared memory.
+// More than 128 tokens: every (token block of 128, column tile) pair is a tile, one launch.
 #include "wq_common.cuh"
 
 namespace dx {
