@@ -32,9 +32,12 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+# The workload: BASELINE's 5B layer set at 83 tokens unless `--workload 14b` (the 14B-shaped
+# set at 913 tokens, the compute-bound regime) is asked for; main() sets these three.
 M_TOKENS = 83
 PRESET = "5b"
 METRIC = "w4a16_5b_layer_set_ms"
+WORKLOADS = {"5b": (83, "w4a16_5b_layer_set_ms"), "14b": (913, "w4a16_14b_layer_set_ms")}
 # DRAM bytes / algorithmic bytes of one wq_gemm_tc launch, from the ncu capture summarised in
 # profiles/wq_gemm_tc_w4_m83_k3072_n14336.md (23.27 MB read for 22.71 MB of packed weights + scales)
 DRAM_OVER_ALGORITHMIC = 1.025
@@ -148,7 +151,7 @@ def run_reference(args) -> int:
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args.gpus),
         "cpu_baseline": {"value": value, "unit": "ms", "cores": threads, "kind": "port",
-                         "sample": "one block (10 of 300 GEMMs) per step, x30; torch CPU op "
+                         "sample": f"one block (10 of {10 * blocks} GEMMs) per step, x{blocks}; torch CPU op "
                                    "sequence of the reference (dequantise whole weight, matmul, bias)"},
         "e2e": {"value": value, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -157,14 +160,18 @@ def run_reference(args) -> int:
 
 
 def workload_config(n_gpus: int) -> dict:
-    return {"workload": "5B backbone linear set: 30 blocks x (self q,k,v,o; cross q,k,v,o; ffn up,down), "
-                        "int4 group 128 symmetric + bias, M=83, seeded random weights",
-            "gemms_per_step": 300, "schedule": "per block: self q,k,v and cross k,v on parallel streams, then o, cross q, cross o, up, down; one CUDA graph per pass", "tokens": M_TOKENS, "dim": 3072, "ffn_dim": 14336,
+    from dexter_labs_b200 import tp
+
+    dim, ffn, blocks = tp.PRESETS[PRESET]
+    set_gb = blocks * (8 * dim * dim + 2 * dim * ffn) * (0.5 + 2.0 / 128) / 1e9
+    return {"workload": f"{PRESET.upper()} backbone linear set: {blocks} blocks x (self q,k,v,o; cross q,k,v,o; "
+                        f"ffn up,down), int4 group 128 symmetric + bias, M={M_TOKENS}, seeded random weights",
+            "gemms_per_step": 10 * blocks, "schedule": "per block: self q,k,v and cross k,v on parallel streams, then o, cross q, cross o, up, down; one CUDA graph per pass", "tokens": M_TOKENS, "dim": dim, "ffn_dim": ffn,
             "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single",
             "collectives": "one NCCL all-reduce (or reduce-scatter + all-gather, --collective rs_ag) after each "
                            "row-parallel linear" if n_gpus > 1 else "none",
-            "l2": "2.53 GB of weights per pass stream through the 126 MB L2; single-GEMM figure rotates "
-                  "16 weight buffers (363 MB)"}
+            "l2": f"{set_gb:.2f} GB of weights per pass stream through the 126 MB L2; single-GEMM figure "
+                  "rotates 16 weight buffers (363 MB)"}
 
 
 # --------------------------------------------------------------------- our arm
@@ -216,7 +223,7 @@ def gemm_figures(d, ops, peaks, m, k, n, bits=4, group=128, rotate=16, reps=7) -
 
 def single_gemm_figures(d, ops, peaks) -> dict:
     """The headline GEMM alone: M=83, K=3072, N=14336, int4 g128, 16 rotating weights."""
-    return gemm_figures(d, ops, peaks, M_TOKENS, 3072, 14336, 4, 128, rotate=16)
+    return gemm_figures(d, ops, peaks, 83, 3072, 14336, 4, 128, rotate=16)
 
 
 def chain_figures(d, ops) -> dict:
@@ -230,7 +237,7 @@ def chain_figures(d, ops) -> dict:
     import torch
 
     torch.manual_seed(0)
-    dim, ffn, m = 3072, 14336, M_TOKENS
+    dim, ffn, m = 3072, 14336, 83
     x = torch.randn(m, dim, device="cuda").to(torch.bfloat16)
     ctx = torch.randn(m, dim, device="cuda").to(torch.bfloat16)
     spec = [(ctx, dim, dim), (x, dim, dim), (x, dim, dim), (x, dim, dim), (ctx, dim, dim),
@@ -462,7 +469,7 @@ def run_ours(args) -> int:
         if rank == 0:
             print(f"fused-qkv variant not timed: {exc}", file=sys.stderr)
 
-    # The same 300 launches strictly one after the other (no parallel streams), as an extra.
+    # The same launches strictly one after the other (no parallel streams), as an extra.
     sequential_ms = None
     try:
         ls.concurrent = False
@@ -496,11 +503,15 @@ def run_ours(args) -> int:
         finish(world, 0)
 
     status = ops.last_status()
-    set_flops = 2.0 * M_TOKENS * (8 * 3072 * 3072 + 2 * 3072 * 14336) * ls.blocks
+    set_flops = 2.0 * M_TOKENS * (8 * ls.dim * ls.dim + 2 * ls.dim * ls.ffn_dim) * ls.blocks
     set_bytes = total_bytes.item()
     launches_per_step = ls.num_gemms
     t_mem_ms = set_bytes / world / (peaks["hbm_gbs"] * 1e6)
-    t_mma_ms = set_flops / world / (peaks["tflops"] * 1e9)
+    # The 5B pass is 300 short kernels (burst peak); the 14B pass at 913 tokens keeps the tensor
+    # pipe busy for tens of milliseconds under the power cap (sustained peak).
+    sustained = PRESET == "14b" and peaks.get("tflops_sustained")
+    tensor_peak = peaks["tflops_sustained"] if sustained else peaks["tflops"]
+    t_mma_ms = set_flops / world / (tensor_peak * 1e9)
     roofline_ms = max(t_mem_ms, t_mma_ms)
     # dominant kernel: wq_gemm_tc<4,false>; per-launch averages over the pass (per rank)
     us_per_launch = ms_per_step * 1e3 / launches_per_step
@@ -508,7 +519,7 @@ def run_ours(args) -> int:
     bytes_per_launch = set_bytes / world / launches_per_step
     bound = "tensor" if t_mma_ms >= t_mem_ms else "hbm"
     if bound == "tensor":
-        achieved, peak, unit = flops_per_launch / us_per_launch * 1e-6, peaks["tflops"], "TFLOP/s"
+        achieved, peak, unit = flops_per_launch / us_per_launch * 1e-6, tensor_peak, "TFLOP/s"
     else:
         achieved, peak, unit = bytes_per_launch / us_per_launch * 1e-3, peaks["hbm_gbs"], "GB/s"
 
@@ -522,12 +533,12 @@ def run_ours(args) -> int:
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
                      "frac": achieved / peak, "traffic": bytes_per_launch * DRAM_OVER_ALGORITHMIC,
-                     "kernel": "wq_gemm_tc<4,false>", "peak_source": f"{peaks['source']} (burst)",
+                     "kernel": "wq_gemm_tc<4,false>", "peak_source": f"{peaks['source']} ({'sustained' if sustained else 'burst'})",
                      "algorithmic_bytes_per_launch": bytes_per_launch,
                      "algorithmic_flops_per_launch": flops_per_launch,
                      "us_per_launch": us_per_launch,
                      "frac_hbm": (bytes_per_launch / us_per_launch * 1e-3) / peaks["hbm_gbs"]},
-        "sequential": {"ms_per_step": sequential_ms, "note": "same 300 launches on one stream"},
+        "sequential": {"ms_per_step": sequential_ms, "note": "the same launches on one stream"},
         "fused_qkv": {"ms_per_step": fused_ms, "launches_per_step": fused.num_gemms,
                       "max_normalised_diff_vs_separate": fused_same,
                       "frac_roofline": None if not fused_ms else roofline_ms / fused_ms},
@@ -540,7 +551,7 @@ def run_ours(args) -> int:
         per_block_ms, threads = cpu_block_ms(1, 3)
         line["cpu_baseline"] = {"value": per_block_ms * ls.blocks, "unit": "ms", "cores": threads,
                                 "kind": "port",
-                                "sample": "one block (10 of 300 GEMMs), median of 3, x30; torch CPU op "
+                                "sample": f"one block (10 of {10 * ls.blocks} GEMMs), median of 3, x{ls.blocks}; torch CPU op "
                                           "sequence of the reference on the host cores"}
     print(json.dumps(line))
     finish(world, 0 if status == 0 else 1)
@@ -558,7 +569,13 @@ def main() -> int:
                     help="time this one GEMM shape only (1 GPU) instead of the layer set; "
                          "`sweep` = M in {1..913} over the 5B linear shapes, int4 and int8")
     ap.add_argument("--reps", type=int, default=7, help="timed repetitions of --gemm (best is kept)")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="5b",
+                    help="5b: the 5B layer set at 83 tokens (the headline); 14b: the 14B-shaped set at "
+                         "913 tokens")
     args = ap.parse_args()
+    global M_TOKENS, PRESET, METRIC
+    PRESET = args.workload
+    M_TOKENS, METRIC = WORKLOADS[PRESET]
     if args.gemm and args.impl == "ours":
         return run_gemm_only(args)
     return run_reference(args) if args.impl == "reference" else run_ours(args)
