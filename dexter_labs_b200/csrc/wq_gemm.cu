@@ -411,18 +411,28 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
               float4 acc[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-              for (int sl = 0; sl < nslots; ++sl) {
-                float4 v[4];
+              // Two slots (eight 16-byte loads) in flight per thread: the reduce is bound by
+              // L2 latency, not bandwidth.  The additions stay in slot order.
+              for (int sl = 0; sl < nslots; sl += 2) {
+                float4 v[8];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const int m = m0 + 4 * j;
-                  v[j] = m < m_rows ? __ldcg(reinterpret_cast<const float4*>(
-                                       tile_ws + sl * slot_elems + m * kTileN + col4))
-                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const int m = m0 + 4 * j;
+                    v[4 * h + j] = (m < m_rows && sl + h < nslots)
+                                       ? __ldcg(reinterpret_cast<const float4*>(
+                                             tile_ws + (sl + h) * slot_elems + m * kTileN + col4))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+                  }
                 }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  acc[j].x += v[j].x; acc[j].y += v[j].y; acc[j].z += v[j].z; acc[j].w += v[j].w;
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    acc[j].x += v[4 * h + j].x; acc[j].y += v[4 * h + j].y;
+                    acc[j].z += v[4 * h + j].z; acc[j].w += v[4 * h + j].w;
+                  }
                 }
               }
 #pragma unroll
@@ -832,9 +842,10 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   DeviceInfo& di = device_info();
   const Plan pl = make_plan(M, N, K, BITS, di.sms, max_ctas);
   if (pl.w_stages < kAStages) return DXB_ERR_UNSUPPORTED;
-  const size_t need = kStatusBytes + counters_bytes(pl.tiles) +
-                      static_cast<size_t>(pl.tiles) * pl.max_slots * pl.NU * kTileN * sizeof(float);
-  if (workspace == nullptr || workspace_bytes < need) return DXB_ERR_WORKSPACE;
+  // Status word and counters are always needed; the partial sums only if the launch ends up
+  // splitting tiles through global scratch (checked below, once the cluster size is known).
+  if (workspace == nullptr || workspace_bytes < kStatusBytes + counters_bytes(pl.tiles))
+    return DXB_ERR_WORKSPACE;
 
   CUtensorMap tq, tx;
   bool ok;
@@ -943,6 +954,11 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
       }
       cache[key] = cluster;
     }
+  }
+  if (cluster == 1) {
+    const size_t need = kStatusBytes + counters_bytes(pl.tiles) +
+                        static_cast<size_t>(pl.tiles) * pl.max_slots * pl.NU * kTileN * sizeof(float);
+    if (workspace_bytes < need) return DXB_ERR_WORKSPACE;
   }
   p.cluster = cluster;
   p.recv_off = pl.recv_off;
@@ -1109,7 +1125,8 @@ int dxb_wq_gemm_static(int bits, const void* x, int64_t ldx, const void* qweight
   {
     const int rows = bits == 4 ? K / 2 : K;
     if (rows >= kUnitRows &&
-        plan_workspace_bytes(M <= 128 ? M : 128, N, K, bits, 0) > kStaticScratchBytes)
+        (plan_workspace_bytes(M <= 128 ? M : 128, N, K, bits, 0) > kStaticScratchBytes ||
+         (M > 128 && plan_workspace_bytes(96, N, K, bits, 0) > kStaticScratchBytes)))
       return DXB_ERR_SCRATCH_LIMIT;
   }
   void* scratch = nullptr;
@@ -1145,8 +1162,11 @@ size_t dxb_workspace_bytes(int M, int N, int K, int bits) {
   if (rows < kUnitRows) return kStatusBytes;
   // Up to 128 tokens: that launch.  More: the larger of the one-launch plan over all token
   // blocks and the plan of a single block (used when the caller's workspace is smaller).
-  const size_t one_block = plan_workspace_bytes(M <= 128 ? M : 128, N, K, bits, 0);
+  size_t one_block = plan_workspace_bytes(M <= 128 ? M : 128, N, K, bits, 0);
   if (M <= 128) return one_block;
+  // block by block, few-tile weights go in blocks of 96 tokens (see dxb_wq_gemm)
+  const size_t block96 = plan_workspace_bytes(96, N, K, bits, 0);
+  if (block96 > one_block) one_block = block96;
   if (static_cast<long long>((N + kTileN - 1) / kTileN) * ((M + 127) / 128) > kMaxTiles)
     return one_block;
   const size_t all_blocks = plan_workspace_bytes(M, N, K, bits, 0);

@@ -284,6 +284,8 @@ class LayerSet:
             self._side = [torch.cuda.Stream() for _ in range(4)]
             self._sms = torch.cuda.get_device_properties(x.device).multi_processor_count
         side = self._side
+        if self.world > 1:
+            return self._block_forward_overlapped(L, x, ctx)
         share = max(self._sms // 5, 1)
         for s in side:
             s.wait_stream(cur)
@@ -295,6 +297,39 @@ class LayerSet:
         cur.wait_stream(side[0])
         cur.wait_stream(side[1])
         x = self._reduce(g(self._row_input(v, L["self_o"]), L["self_o"].weight))
+        g(x, L["cross_q"].weight)
+        cur.wait_stream(side[2])
+        cur.wait_stream(side[3])
+        x = self._reduce(g(self._row_input(outs["cross_v"], L["cross_o"]), L["cross_o"].weight))
+        h = g(x, L["ffn_up"].weight)
+        x = self._reduce(g(self._row_input(h, L["ffn_down"]), L["ffn_down"].weight))
+        return x
+
+    def _block_forward_overlapped(self, L, x: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
+        """Schedule for more than one rank: the collective after self o is the place where the
+        GPU would otherwise wait for NVLink, so cross k and cross v (which only need the
+        context) are held back until self o's GEMM has been issued and then run on two side
+        streams while that collective is in flight on the main stream."""
+        g = self.gemm
+        cur = torch.cuda.current_stream()
+        side = self._side
+        third = max(self._sms // 3, 1)
+        half = max(self._sms // 2, 1)
+        for s in side[:2]:
+            s.wait_stream(cur)
+        for s, name in zip(side[:2], ("self_q", "self_k")):
+            with torch.cuda.stream(s):
+                g(x, L[name].weight, third)
+        v = g(x, L["self_v"].weight, third)
+        cur.wait_stream(side[0])
+        cur.wait_stream(side[1])
+        partial = g(self._row_input(v, L["self_o"]), L["self_o"].weight)
+        outs = {}
+        for s, name in zip(side[2:], ("cross_k", "cross_v")):
+            s.wait_stream(cur)  # after self o's GEMM, alongside its collective
+            with torch.cuda.stream(s):
+                outs[name] = g(ctx, L[name].weight, half)
+        x = self._reduce(partial)
         g(x, L["cross_q"].weight)
         cur.wait_stream(side[2])
         cur.wait_stream(side[3])

@@ -33,6 +33,11 @@ def _worker(rank, world, port, results):
         y = ls.forward(x, ctx)
         torch.cuda.synchronize()
         results[rank] = y.float().cpu().numpy()
+        # the overlapped multi-stream schedule computes the same linears
+        ls.concurrent = True
+        y2 = ls.forward(x, ctx)
+        torch.cuda.synchronize()
+        results[rank + world] = y2.float().cpu().numpy()
     finally:
         dist.destroy_process_group()
 
@@ -50,6 +55,6 @@ def test_two_gpu_layer_set_matches_one_gpu(b200_lib):
     world = 2
     results = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
-    for rank in range(world):
+    for rank in range(2 * world):
         e = np.abs(results[rank] - want).max() / max(np.abs(want).max(), 1e-6)
         assert e < 1e-2, (rank, e)
