@@ -159,7 +159,7 @@ def run_reference(args) -> int:
     return 0
 
 
-def workload_config(n_gpus: int) -> dict:
+def workload_config(n_gpus: int, collective: str = "all_reduce") -> dict:
     from dexter_labs_b200 import tp
 
     dim, ffn, blocks = tp.PRESETS[PRESET]
@@ -168,8 +168,11 @@ def workload_config(n_gpus: int) -> dict:
                         f"ffn up,down), int4 group 128 symmetric + bias, M={M_TOKENS}, seeded random weights",
             "gemms_per_step": 10 * blocks, "schedule": "per block: self q,k,v and cross k,v on parallel streams, then o, cross q, cross o, up, down; one CUDA graph per pass", "tokens": M_TOKENS, "dim": dim, "ffn_dim": ffn,
             "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single",
-            "collectives": "one NCCL all-reduce (or reduce-scatter + all-gather, --collective rs_ag) after each "
-                           "row-parallel linear" if n_gpus > 1 else "none",
+            "collectives": {"all_reduce": "one NCCL all-reduce after each row-parallel linear",
+                            "rs_ag": "NCCL reduce-scatter + all-gather after each row-parallel linear",
+                            "peer": "one all-reduce kernel of this library over NVLink peer memory after "
+                                    "each row-parallel linear (NCCL above 1 MB)"}[collective]
+                           if n_gpus > 1 else "none",
             "l2": f"{set_gb:.2f} GB of weights per pass stream through the 126 MB L2; single-GEMM figure "
                   "rotates 16 weight buffers (363 MB)"}
 
@@ -364,8 +367,14 @@ def run_ours(args) -> int:
 
     peaks = load_peaks()
     ls = tp.LayerSet.build(PRESET, rank=rank, world=world, bits=4, group_size=128, symmetric=True,
-                           bias=True, device=f"cuda:{local}", seed=0, collective=args.collective,
+                           bias=True, device=f"cuda:{local}", seed=0,
+                           collective="all_reduce" if args.collective == "peer" else args.collective,
                            concurrent=True)
+    if world > 1 and args.collective == "peer":
+        # own all-reduce kernel over NVLink peer memory (messages up to 1 MB); NCCL otherwise
+        if not ls.enable_peer_reduce(M_TOKENS, f"cuda:{local}") and rank == 0:
+            print(f"peer all-reduce unavailable ({getattr(ls, '_peer_error', '?')}); using NCCL",
+                  file=sys.stderr)
     torch.manual_seed(0)
     host_x = torch.randn(M_TOKENS, ls.dim).to(torch.bfloat16).pin_memory()
     host_ctx = torch.randn(M_TOKENS, ls.dim).to(torch.bfloat16).pin_memory()
@@ -442,7 +451,8 @@ def run_ours(args) -> int:
     # summation order; 7 launches per block instead of 10); reported as an extra.
     fused = tp.LayerSet(dim=ls.dim, ffn_dim=ls.ffn_dim, blocks=ls.blocks, rank=rank, world=world,
                         bits=ls.bits, group_size=ls.group_size, collective=ls.collective,
-                        fuse_qkv=True, layers=[tp.LayerSet._fuse(r) for r in ls.layers])
+                        fuse_qkv=True, layers=[tp.LayerSet._fuse(r) for r in ls.layers],
+                        _peer=ls._peer)
     yf = fused.forward(x, ctx)
     torch.cuda.synchronize()
     fused_ms = None
@@ -526,7 +536,7 @@ def run_ours(args) -> int:
     line = {
         "metric": METRIC, "value": ms_per_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
         "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world, ls.collective),
         "clocks": clocks,
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": 2 * host_x.numel() * 2,
                 "d2h_bytes_per_step": host_y.numel() * 2},
@@ -563,7 +573,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    ap.add_argument("--collective", choices=("all_reduce", "rs_ag"), default="all_reduce",
+    ap.add_argument("--collective", choices=("all_reduce", "rs_ag", "peer"), default="all_reduce",
                     help="how row-parallel partial sums are combined when N > 1")
     ap.add_argument("--gemm", default=None, metavar="M,K,N[,bits[,group]] | sweep | chain",
                     help="time this one GEMM shape only (1 GPU) instead of the layer set; "

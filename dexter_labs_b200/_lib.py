@@ -31,6 +31,9 @@ class ChainItem(ctypes.Structure):
 
 # name -> (restype, argtypes); one entry per symbol declared in include/dexter_b200.h
 SIGNATURES = {
+    "dxb_peer_allreduce_bytes": (c_size_t, [c_int, c_int64]),
+    "dxb_peer_allreduce": (c_int, [c_void_p, c_void_p, c_int64, ctypes.POINTER(c_void_p), c_int64,
+                                   c_int, c_int, c_void_p, c_void_p]),
     "dxb_chain_workspace_bytes": (c_size_t, [c_int, ctypes.POINTER(ChainItem), c_int, c_int]),
     "dxb_wq_gemm_chain": (c_int, [c_int, ctypes.POINTER(ChainItem), c_int, c_void_p, c_size_t,
                                   c_int, c_void_p]),

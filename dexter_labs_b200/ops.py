@@ -22,7 +22,7 @@ from .platform import ArchVersion, Capability
 from .registry import Priority, register, select
 
 __all__ = ["w4a16", "w8a16", "linear", "dequantize", "accepts", "KERNEL_NAMES", "register_with",
-           "last_status", "chain", "chain_status", "ChainLink", "CHAIN_MAX"]
+           "last_status", "chain", "chain_status", "ChainLink", "CHAIN_MAX", "PeerAllReduce"]
 
 KERNEL_NAMES = {"w4a16": "b200_w4a16_tcgen05", "w8a16": "b200_w8a16_tcgen05"}
 
@@ -242,6 +242,62 @@ def chain_status(device: Optional[torch.device] = None) -> int:
         if ws is None:
             return _lib.OK
         return _LIB.dxb_read_status(ws.data_ptr(), ctypes.c_void_p(stream))
+
+
+class PeerAllReduce:
+    """Sum of bf16 partial outputs over the ranks of one NVLink domain (``dxb_peer_allreduce``).
+
+    Built once per process group (a collective: every rank must construct it at the same
+    point): allocates this rank's region of peer-mapped memory through
+    ``torch.distributed._symmetric_memory``, zero-fills it and exchanges the mappings.
+    ``__call__(partial)`` then returns the full sum on every rank with one kernel launch on
+    the current stream; all ranks must make the same calls in the same order.
+    """
+
+    MAX_BYTES = 1 << 20  # larger messages belong to the library collectives
+
+    def __init__(self, group, capacity_elems: int, device: torch.device) -> None:
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.capacity = (int(capacity_elems) + 7) // 8 * 8
+        nbytes = _LIB.dxb_peer_allreduce_bytes(self.world, self.capacity)
+        if nbytes == 0:
+            raise RuntimeError("peer all-reduce supports at most 8 ranks")
+        name = group.group_name
+        # plain peer mappings are all the kernel uses: keep the region off NVLink multicast
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        with torch.cuda.device(device):
+            self.region = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+            self.region.zero_()
+            self.handle = symm_mem.rendezvous(self.region, name)
+            self.status = torch.zeros(1, dtype=torch.int32, device=device)
+            torch.cuda.synchronize()
+        dist.barrier(group)  # every region is zero before anyone's first call
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self._ptrs = (ctypes.c_void_p * self.world)(*ptrs)
+
+    def __call__(self, partial: torch.Tensor) -> torch.Tensor:
+        if partial.dtype != torch.bfloat16 or not partial.is_contiguous():
+            raise RuntimeError("peer all-reduce takes contiguous bf16 tensors")
+        n = partial.numel()
+        if n % 8 or n > self.capacity:
+            raise ValueError(f"peer all-reduce: {n} elements (capacity {self.capacity}, multiple of 8)")
+        out = torch.empty_like(partial)
+        with torch.cuda.device(partial.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            rc = _LIB.dxb_peer_allreduce(partial.data_ptr(), out.data_ptr(), n, self._ptrs,
+                                         self.capacity, self.rank, self.world,
+                                         self.status.data_ptr(), ctypes.c_void_p(stream))
+        if rc != _lib.OK:
+            _raise(rc)
+        return out
+
+    def check(self) -> int:
+        """Synchronise and return the error word (0, or DXB_ERR_KERNEL_TIMEOUT)."""
+        return int(self.status.item())
 
 
 def dequantize(qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor],

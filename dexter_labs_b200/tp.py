@@ -162,7 +162,7 @@ class LayerSet:
     world: int = 1
     bits: int = 4
     group_size: int = 128
-    collective: str = "rs_ag"  # "rs_ag" | "all_reduce"
+    collective: str = "rs_ag"  # "rs_ag" | "all_reduce" | "peer" (own kernel over peer memory)
     fuse_qkv: bool = False     # one launch for self q,k,v and one for cross k,v (N-concatenation)
     concurrent: bool = False   # independent linears of a block on parallel CUDA streams
     layers: List[List[ShardedLinear]] = field(default_factory=list)
@@ -171,6 +171,34 @@ class LayerSet:
     _pad: Dict[Tuple[int, int], torch.Tensor] = field(default_factory=dict)
     _side: Optional[list] = None
     _sms: int = 0
+    _peer: Optional[object] = None  # ops.PeerAllReduce, see enable_peer_reduce
+
+    def enable_peer_reduce(self, tokens: int, device) -> bool:
+        """Set up the peer-memory all-reduce for outputs of up to ``tokens x dim`` bf16.
+
+        A collective: every rank calls it at the same point.  Returns False (and the set
+        keeps using NCCL's all-reduce) when peer-mapped memory cannot be set up on any rank.
+        """
+        import torch.distributed as dist
+
+        from . import ops
+
+        group = self.process_group if self.process_group is not None else dist.group.WORLD
+        peer, ok = None, 1
+        try:
+            peer = ops.PeerAllReduce(group, tokens * self.dim, torch.device(device))
+        except Exception as exc:  # noqa: BLE001 - reported below, every rank must agree
+            ok = 0
+            self._peer_error = repr(exc)
+        flag = torch.tensor([ok], device=device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if int(flag.item()) == 1:
+            self._peer = peer
+            self.collective = "peer"
+            return True
+        self._peer = None
+        self.collective = "all_reduce"
+        return False
 
     # ------------------------------------------------------------------ build
     @classmethod
@@ -251,6 +279,15 @@ class LayerSet:
             return partial
         import torch.distributed as dist
 
+        if self.collective == "peer":
+            # one kernel over NVLink peer memory for the small messages of the few-token
+            # regime; anything larger goes to NCCL
+            nbytes = partial.numel() * partial.element_size()
+            if self._peer is not None and nbytes <= self._peer.MAX_BYTES and partial.numel() % 8 == 0 \
+                    and partial.numel() <= self._peer.capacity:
+                return self._peer(partial.contiguous())
+            dist.all_reduce(partial, group=self.process_group)
+            return partial
         if self.collective == "all_reduce":
             dist.all_reduce(partial, group=self.process_group)
             return partial

@@ -151,6 +151,30 @@ size_t dxb_chain_workspace_bytes(int bits, const dxb_chain_item* items, int n_it
 int dxb_wq_gemm_chain(int bits, const dxb_chain_item* items, int n_items, void* workspace,
                       size_t workspace_bytes, int max_ctas, void* cuda_stream);
 
+/*
+ * Tensor-parallel glue for the few-token regime: sum of the row-parallel linears' partial
+ * outputs over the ranks of one NVLink domain, every rank receiving the full sum.  The
+ * reference has no tensor parallelism, so this replaces nothing there; it stands where a
+ * library all-reduce would, which at 83 x 3072 bf16 (0.5 MB) is mostly latency.
+ *
+ * peer_regions[r] = rank r's region of peer-mapped memory AS MAPPED IN THIS PROCESS (host
+ * array of `world` device pointers, 16-byte aligned), each dxb_peer_allreduce_bytes(world,
+ * capacity_elems) bytes, zero-filled on every rank before anyone's first call and used for
+ * nothing else.  `partial` and `out` are ordinary local buffers of `elems` bf16 (elems a
+ * multiple of 8, <= capacity_elems).  All ranks must make the same sequence of calls with
+ * the same `elems`; each rank runs on its own GPU.  One kernel per call: plain 16-byte
+ * stores into the peers' regions, system-scope release/acquire flags, a bounded wait (about
+ * a second, then DXB_ERR_KERNEL_TIMEOUT in *status, a local int, may be NULL), the sum in
+ * fp32 in rank order (identical bits on every rank), one rounding to bf16.  The call does
+ * not allocate or synchronise and can be captured in a CUDA graph and replayed.
+ * world <= 8.  Meant for messages up to about 1 MB; larger ones belong to the library
+ * collectives (every rank sends its whole partial to every peer).
+ */
+size_t dxb_peer_allreduce_bytes(int world, int64_t capacity_elems);
+int dxb_peer_allreduce(const void* partial, void* out, int64_t elems, void* const* peer_regions,
+                       int64_t capacity_elems, int rank, int world, void* status,
+                       void* cuda_stream);
+
 /* Bytes of workspace dxb_wq_gemm needs for this problem on the current device. */
 size_t dxb_workspace_bytes(int M, int N, int K, int bits);
 

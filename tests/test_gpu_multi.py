@@ -38,6 +38,24 @@ def _worker(rank, world, port, results):
         y2 = ls.forward(x, ctx)
         torch.cuda.synchronize()
         results[rank + world] = y2.float().cpu().numpy()
+        # own all-reduce kernel over peer-mapped memory instead of NCCL, eagerly and as a
+        # replayed CUDA graph (the epoch lives on the device, so replays keep working)
+        if ls.enable_peer_reduce(83, f"cuda:{rank}"):
+            y3 = ls.forward(x, ctx)
+            torch.cuda.synchronize()
+            results[rank + 2 * world] = y3.float().cpu().numpy()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                y4 = ls.forward(x, ctx)
+            for _ in range(3):
+                y4.zero_()
+                graph.replay()
+                torch.cuda.synchronize()
+                assert torch.equal(y4, y3)
+            assert ls._peer.check() == 0
+            results["peer"] = True
+        else:
+            results["peer_error"] = getattr(ls, "_peer_error", "unknown")
     finally:
         dist.destroy_process_group()
 
@@ -55,6 +73,9 @@ def test_two_gpu_layer_set_matches_one_gpu(b200_lib):
     world = 2
     results = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
-    for rank in range(2 * world):
+    assert results.get("peer"), f"peer all-reduce could not be set up: {results.get('peer_error')}"
+    for rank in range(3 * world):
         e = np.abs(results[rank] - want).max() / max(np.abs(want).max(), 1e-6)
         assert e < 1e-2, (rank, e)
+    # every rank holds the same bits after the peer all-reduce (fixed summation order)
+    assert np.array_equal(results[2 * world], results[2 * world + 1])
