@@ -370,7 +370,7 @@ def run_ours(args) -> int:
                            bias=True, device=f"cuda:{local}", seed=0,
                            collective="all_reduce" if args.collective == "peer" else args.collective,
                            concurrent=True)
-    if world > 1 and args.collective == "peer":
+    if world > 1 and args.collective == "peer" and M_TOKENS * ls.dim * 2 <= ops.PeerAllReduce.MAX_BYTES:
         # own all-reduce kernel over NVLink peer memory (messages up to 1 MB); NCCL otherwise
         if not ls.enable_peer_reduce(M_TOKENS, f"cuda:{local}") and rank == 0:
             print(f"peer all-reduce unavailable ({getattr(ls, '_peer_error', '?')}); using NCCL",
@@ -573,7 +573,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    ap.add_argument("--collective", choices=("all_reduce", "rs_ag", "peer"), default="all_reduce",
+    ap.add_argument("--collective", choices=("all_reduce", "rs_ag", "peer"), default="peer",
                     help="how row-parallel partial sums are combined when N > 1")
     ap.add_argument("--gemm", default=None, metavar="M,K,N[,bits[,group]] | sweep | chain",
                     help="time this one GEMM shape only (1 GPU) instead of the layer set; "
