@@ -283,6 +283,64 @@ def chain_figures(d, ops) -> dict:
             "note": "weights of one block (84 MB) stay in the 126 MB L2 across replays in both arms"}
 
 
+def run_allreduce_only(args) -> int:
+    """``--gemm allreduce`` under torch.distributed.run: the 83 x 3072 bf16 sum over ranks with
+    the library's peer-memory kernel against NCCL's all-reduce, back to back in a CUDA graph."""
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world < 2:
+        print("--gemm allreduce needs torch.distributed.run with at least 2 ranks", file=sys.stderr)
+        return 2
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from dexter_labs_b200 import ops
+
+    torch.manual_seed(rank)
+    x = torch.randn(83, 3072, device="cuda").to(torch.bfloat16)
+    peer = ops.PeerAllReduce(dist.group.WORLD, x.numel(), torch.device("cuda", local))
+    y = x.clone()
+
+    def time_us(fn, per=20, replays=10):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(per):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item() * 1e3 / (per * replays)
+
+    peer_us = time_us(lambda: peer(x))
+    nccl_us = time_us(lambda: dist.all_reduce(y))
+    want = x.clone()
+    dist.all_reduce(want)
+    got = peer(x)
+    torch.cuda.synchronize()
+    diff = float((got.float() - want.float()).abs().max() / want.float().abs().max().clamp_min(1e-6))
+    if rank == 0:
+        print(json.dumps({"metric": "allreduce_83x3072_bf16_us", "n_gpus": world, "peer_us": peer_us,
+                          "nccl_us": nccl_us, "max_normalised_diff_vs_nccl": diff,
+                          "peer_status": peer.check()}), flush=True)
+    finish(world, 0)
+    return 0
+
+
 SWEEP_SHAPES = (("qkv", 3072, 9216), ("o", 3072, 3072), ("up", 3072, 14336), ("down", 14336, 3072))
 SWEEP_M = (1, 8, 32, 83, 256, 512, 913)
 
@@ -575,7 +633,7 @@ def main() -> int:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--collective", choices=("all_reduce", "rs_ag", "peer"), default="peer",
                     help="how row-parallel partial sums are combined when N > 1")
-    ap.add_argument("--gemm", default=None, metavar="M,K,N[,bits[,group]] | sweep | chain",
+    ap.add_argument("--gemm", default=None, metavar="M,K,N[,bits[,group]] | sweep | chain | allreduce",
                     help="time this one GEMM shape only (1 GPU) instead of the layer set; "
                          "`sweep` = M in {1..913} over the 5B linear shapes, int4 and int8")
     ap.add_argument("--reps", type=int, default=7, help="timed repetitions of --gemm (best is kept)")
@@ -586,6 +644,8 @@ def main() -> int:
     global M_TOKENS, PRESET, METRIC
     PRESET = args.workload
     M_TOKENS, METRIC = WORKLOADS[PRESET]
+    if args.gemm == "allreduce" and args.impl == "ours":
+        return run_allreduce_only(args)
     if args.gemm and args.impl == "ours":
         return run_gemm_only(args)
     return run_reference(args) if args.impl == "reference" else run_ours(args)
