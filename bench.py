@@ -32,7 +32,7 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# The workload: BASELINE's 5B layer set at 83 tokens unless `--workload 14b` (the 14B-shaped
+# The workload: the 5B layer set at 83 tokens unless `--workload 14b` (the 14B-shaped
 # set at 913 tokens, the compute-bound regime) is asked for; main() sets these three.
 M_TOKENS = 83
 PRESET = "5b"

@@ -254,7 +254,7 @@ def test_back_to_back_launches_with_dependent_launch(d, oracle):
     assert torch.isfinite(got.float()).all()
 
 
-# ------------------------------------------- 14B-shaped linears at M = 913 (BASELINE config 5)
+# ------------------------------------------- 14B-shaped linears at M = 913
 @pytest.mark.parametrize("shape", [("qkv_like", 5120, 5120), ("up", 5120, 13824), ("down", 13824, 5120)])
 def test_14b_shapes_m913(shape, d, oracle):
     _, k, n = shape
