@@ -166,7 +166,13 @@ def workload_config(n_gpus: int, collective: str = "all_reduce") -> dict:
     set_gb = blocks * (8 * dim * dim + 2 * dim * ffn) * (0.5 + 2.0 / 128) / 1e9
     return {"workload": f"{PRESET.upper()} backbone linear set: {blocks} blocks x (self q,k,v,o; cross q,k,v,o; "
                         f"ffn up,down), int4 group 128 symmetric + bias, M={M_TOKENS}, seeded random weights",
-            "gemms_per_step": 10 * blocks, "schedule": "per block: self q,k,v and cross k,v on parallel streams, then o, cross q, cross o, up, down; one CUDA graph per pass", "tokens": M_TOKENS, "dim": dim, "ffn_dim": ffn,
+            "gemms_per_step": (10 if n_gpus == 1 else 7) * blocks,
+            "schedule": ("per block: self q,k,v and cross k,v on parallel streams, then o, cross q, cross o, "
+                         "up, down; one CUDA graph per pass") if n_gpus == 1 else
+                        ("per block: self q,k,v as one launch, o, [its collective | cross k,v as one launch on a "
+                         "side stream], cross q, cross o + collective, up, down + collective; one CUDA graph "
+                         "per pass"),
+            "tokens": M_TOKENS, "dim": dim, "ffn_dim": ffn,
             "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single",
             "collectives": {"all_reduce": "one NCCL all-reduce after each row-parallel linear",
                             "rs_ag": "NCCL reduce-scatter + all-gather after each row-parallel linear",
@@ -427,7 +433,7 @@ def run_ours(args) -> int:
     ls = tp.LayerSet.build(PRESET, rank=rank, world=world, bits=4, group_size=128, symmetric=True,
                            bias=True, device=f"cuda:{local}", seed=0,
                            collective="all_reduce" if args.collective == "peer" else args.collective,
-                           concurrent=True)
+                           concurrent=True, fuse_qkv=world > 1)
     if world > 1 and args.collective == "peer" and M_TOKENS * ls.dim * 2 <= ops.PeerAllReduce.MAX_BYTES:
         # own all-reduce kernel over NVLink peer memory (messages up to 1 MB); NCCL otherwise
         if not ls.enable_peer_reduce(M_TOKENS, f"cuda:{local}") and rank == 0:
@@ -504,37 +510,34 @@ def run_ours(args) -> int:
     e2e_ms = e2e.item() / args.steps
     clocks = sampler.stop() if rank == 0 else None
 
-    # Same linears with self q/k/v and cross k/v each issued as one N-concatenated launch
-    # (same arithmetic per column, but another K-split order, so equal only up to fp32
-    # summation order; 7 launches per block instead of 10); reported as an extra.
-    fused = tp.LayerSet(dim=ls.dim, ffn_dim=ls.ffn_dim, blocks=ls.blocks, rank=rank, world=world,
-                        bits=ls.bits, group_size=ls.group_size, collective=ls.collective,
-                        fuse_qkv=True, layers=[tp.LayerSet._fuse(r) for r in ls.layers],
-                        _peer=ls._peer)
-    yf = fused.forward(x, ctx)
-    torch.cuda.synchronize()
-    fused_ms = None
-    try:
-        fgraph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(fgraph):
+    # One GPU only: the same linears with self q/k/v and cross k/v each issued as one
+    # N-concatenated launch (same arithmetic per column, but another K-split order, so equal
+    # only up to fp32 summation order; 7 launches per block instead of 10), as an extra.
+    # With more than one rank the main arm above already is that fused schedule.
+    fused_ms, fused_same, fused_launches = None, None, None
+    if world == 1:
+        try:
+            fused = tp.LayerSet(dim=ls.dim, ffn_dim=ls.ffn_dim, blocks=ls.blocks, rank=rank, world=world,
+                                bits=ls.bits, group_size=ls.group_size, collective=ls.collective,
+                                fuse_qkv=True, layers=[tp.LayerSet._fuse(r) for r in ls.layers])
+            fused_launches = fused.num_gemms
             yf = fused.forward(x, ctx)
-        for _ in range(3):
-            fgraph.replay()
-        barrier()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        for _ in range(args.steps):
-            fgraph.replay()
-        g1.record()
-        barrier()
-        ft = torch.tensor([g0.elapsed_time(g1)], device="cuda")
-        if world > 1:
-            dist.all_reduce(ft, op=dist.ReduceOp.MAX)
-        fused_ms = ft.item() / args.steps
-        fused_same = float((yf.float() - y.float()).abs().max() / y.float().abs().max().clamp(min=1e-6))
-    except Exception as exc:  # noqa: BLE001
-        fused_same = None
-        if rank == 0:
+            torch.cuda.synchronize()
+            fgraph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(fgraph):
+                yf = fused.forward(x, ctx)
+            for _ in range(3):
+                fgraph.replay()
+            barrier()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record()
+            for _ in range(args.steps):
+                fgraph.replay()
+            g1.record()
+            barrier()
+            fused_ms = g0.elapsed_time(g1) / args.steps
+            fused_same = float((yf.float() - y.float()).abs().max() / y.float().abs().max().clamp(min=1e-6))
+        except Exception as exc:  # noqa: BLE001
             print(f"fused-qkv variant not timed: {exc}", file=sys.stderr)
 
     # The same launches strictly one after the other (no parallel streams), as an extra.
@@ -598,7 +601,8 @@ def run_ours(args) -> int:
         "clocks": clocks,
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": 2 * host_x.numel() * 2,
                 "d2h_bytes_per_step": host_y.numel() * 2},
-        "gpu_launches": launches_per_step * args.steps,
+        # GEMM launches, plus this library's all-reduce kernel after each row-parallel linear
+        "gpu_launches": (launches_per_step + (3 * ls.blocks if ls._peer is not None else 0)) * args.steps,
         "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
                      "frac": achieved / peak, "traffic": bytes_per_launch * DRAM_OVER_ALGORITHMIC,
                      "kernel": "wq_gemm_tc<4,false>", "peak_source": f"{peaks['source']} ({'sustained' if sustained else 'burst'})",
@@ -607,7 +611,7 @@ def run_ours(args) -> int:
                      "us_per_launch": us_per_launch,
                      "frac_hbm": (bytes_per_launch / us_per_launch * 1e-3) / peaks["hbm_gbs"]},
         "sequential": {"ms_per_step": sequential_ms, "note": "the same launches on one stream"},
-        "fused_qkv": {"ms_per_step": fused_ms, "launches_per_step": fused.num_gemms,
+        "fused_qkv": {"ms_per_step": fused_ms, "launches_per_step": fused_launches,
                       "max_normalised_diff_vs_separate": fused_same,
                       "frac_roofline": None if not fused_ms else roofline_ms / fused_ms},
         "layer_set": {"weight_bytes": set_bytes, "flops": set_flops, "roofline_ms": roofline_ms,

@@ -375,10 +375,37 @@ class LayerSet:
         x = self._reduce(g(self._row_input(h, L["ffn_down"]), L["ffn_down"].weight))
         return x
 
+    def _block_forward_fused_overlapped(self, blk: int, x: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
+        """More than one rank, q/k/v fused: seven launches per block, and the fused cross k/v
+        launch (context only) runs on a side stream while self o's collective is in flight."""
+        L = {l.name: l for l in self.layers[blk]}
+        g = self.gemm
+        cur = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = [torch.cuda.Stream() for _ in range(4)]
+            self._sms = torch.cuda.get_device_properties(x.device).multi_processor_count
+        side = self._side[0]
+        qkv = g(x, L["self_qkv"].weight)
+        v = qkv[:, 2 * (qkv.shape[1] // 3):]
+        partial = g(self._row_input(v, L["self_o"]), L["self_o"].weight)
+        side.wait_stream(cur)  # after self o's GEMM, alongside its collective
+        with torch.cuda.stream(side):
+            kv = g(ctx, L["cross_kv"].weight, max(self._sms // 2, 1))
+        x = self._reduce(partial)
+        g(x, L["cross_q"].weight)
+        cur.wait_stream(side)
+        cv = kv[:, kv.shape[1] // 2:]
+        x = self._reduce(g(self._row_input(cv, L["cross_o"]), L["cross_o"].weight))
+        h = g(x, L["ffn_up"].weight)
+        x = self._reduce(g(self._row_input(h, L["ffn_down"]), L["ffn_down"].weight))
+        return x
+
     def block_forward(self, blk: int, x: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
         """x, ctx: ``[M, dim]`` replicated on every rank; returns the new replicated x."""
         if self.concurrent and not self.fuse_qkv and x.is_cuda:
             return self._block_forward_concurrent(blk, x, ctx)
+        if self.concurrent and self.fuse_qkv and self.world > 1 and x.is_cuda:
+            return self._block_forward_fused_overlapped(blk, x, ctx)
         L = {l.name: l for l in self.layers[blk]}
         g = self.gemm
         # self attention: q, k, v column-parallel; the v shard stands in for the attention output

@@ -56,6 +56,12 @@ def _worker(rank, world, port, results):
             results["peer"] = True
         else:
             results["peer_error"] = getattr(ls, "_peer_error", "unknown")
+        # q/k/v fused into one launch, cross k/v overlapped with self o's collective
+        fused = tp.LayerSet.build("5b", blocks=1, rank=rank, world=world, seed=3, device=f"cuda:{rank}",
+                                  fuse_qkv=True, concurrent=True, collective="all_reduce")
+        y5 = fused.forward(x, ctx)
+        torch.cuda.synchronize()
+        results[rank + 3 * world] = y5.float().cpu().numpy()
     finally:
         dist.destroy_process_group()
 
@@ -74,7 +80,7 @@ def test_two_gpu_layer_set_matches_one_gpu(b200_lib):
     results = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
     assert results.get("peer"), f"peer all-reduce could not be set up: {results.get('peer_error')}"
-    for rank in range(3 * world):
+    for rank in range(4 * world):
         e = np.abs(results[rank] - want).max() / max(np.abs(want).max(), 1e-6)
         assert e < 1e-2, (rank, e)
     # every rank holds the same bits after the peer all-reduce (fixed summation order)
