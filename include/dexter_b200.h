@@ -55,6 +55,8 @@ enum {
  * that may overlap on the GPU need different workspaces.
  * `max_ctas` <= 0 lets the library use every SM; a positive value caps the grid, so
  * that several independent GEMMs can run side by side on different streams.
+ * Any M: up to 128 tokens are one accumulator block; more tokens are processed as blocks of
+ * 128 inside ONE launch (every (token block, 128-column tile) pair is a tile of the grid).
  */
 int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const void* scales,
                 const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
@@ -175,7 +177,10 @@ int dxb_peer_allreduce(const void* partial, void* out, int64_t elems, void* cons
                        int64_t capacity_elems, int rank, int world, void* status,
                        void* cuda_stream);
 
-/* Bytes of workspace dxb_wq_gemm needs for this problem on the current device. */
+/* Bytes of workspace dxb_wq_gemm needs for this problem on the current device.  For more
+ * than 128 tokens this is what the one-launch plan over all token blocks needs; dxb_wq_gemm
+ * also accepts the smaller amount a 128-token (and 96-token) problem asks for and then
+ * launches block by block. */
 size_t dxb_workspace_bytes(int M, int N, int K, int bits);
 
 /*
