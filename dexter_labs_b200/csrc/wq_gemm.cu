@@ -68,6 +68,9 @@ struct WqParams {
   int group_shift;     // log2(group / 64) when that is a power of two, else -1
   int cluster;         // CTAs per tile (thread-block cluster along x); 1 = no cluster
   int recv_off;        // cluster mode: byte offset of the receive buffers in shared memory
+  int recv_alias;      // cluster mode: the receive buffers lie over the (then idle) rings, so
+                       // partial rows are only sent once every CTA of the cluster has finished
+                       // its main loop
   int rows_per;        // cluster mode: token rows each CTA of the cluster reduces
   int rows_inv;        // ceil(65536 / rows_per): row / rows_per == (row * rows_inv) >> 16
   long long* trace;    // only used when built with -DDXB_TRACE
@@ -139,6 +142,29 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const int tile_begin = u_begin / U;
   const int ku_begin = u_begin - tile_begin * U;
   volatile int* abortp = &abort_flag;
+
+  // Cluster mode: send this CTA's fp32 partial rows from accumulator `d_tmem` (already
+  // offset to the calling warp's lane quadrant) to their owners' receive buffers.
+  auto cluster_send = [&](uint32_t d_tmem, int c, int n_local) {
+    const uint32_t recv0 = smem0 + static_cast<uint32_t>(p.recv_off);
+    for (int c0 = 0; c0 < p.NU; c0 += 16) {
+      uint32_t ra[8], rb[8];
+      tmem_ld_16x128b_x4(d_tmem + c0, ra);
+      tmem_ld_16x128b_x4(d_tmem + (16u << 16) + c0, rb);
+      tc_wait_ld();
+#pragma unroll
+      for (int rep = 0; rep < 4; ++rep) {
+        const int m = c0 + 4 * rep + c;
+        if (m < p.M) {
+          const int owner = (m * p.rows_inv) >> 16;
+          const int row = crank * p.rows_per + (m - owner * p.rows_per);
+          st_dsmem_b32x4(dsmem_addr(recv0 + static_cast<uint32_t>(row * kTileN + n_local) * 4u, owner),
+                         ra[2 * rep], ra[2 * rep + 1], rb[2 * rep], rb[2 * rep + 1]);
+        }
+      }
+    }
+  };
+  int pending_acc = -1;  // epilogue warps, cluster mode with aliased receive buffers
 
   if (warp == 0 || warp == 3) {
     // ============================================ TMA producer: packed weights
@@ -340,26 +366,17 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         // of the tile.  Every CTA sends each owner its fp32 partial rows straight from the
         // accumulator registers into the owner's receive buffer `crank` (distributed shared
         // memory stores); one cluster barrier later the owner only reads its own memory.
-        const uint32_t recv0 = smem0 + static_cast<uint32_t>(p.recv_off);
-        for (int c0 = 0; c0 < p.NU; c0 += 16) {
-          uint32_t ra[8], rb[8];
-          tmem_ld_16x128b_x4(d_tmem + c0, ra);
-          tmem_ld_16x128b_x4(d_tmem + (16u << 16) + c0, rb);
-          tc_wait_ld();
-#pragma unroll
-          for (int rep = 0; rep < 4; ++rep) {
-            const int m = c0 + 4 * rep + c;
-            if (m < p.M) {
-              const int owner = (m * p.rows_inv) >> 16;
-              const int row = crank * p.rows_per + (m - owner * p.rows_per);
-              st_dsmem_b32x4(dsmem_addr(recv0 + static_cast<uint32_t>(row * kTileN + n_local) * 4u, owner),
-                             ra[2 * rep], ra[2 * rep + 1], rb[2 * rep], rb[2 * rep + 1]);
-            }
-          }
+        if (p.recv_alias) {
+          // The receive buffers lie over the rings, which the peers may still be using: the
+          // rows are sent at the end of the kernel, after a cluster barrier (a cluster CTA
+          // has exactly this one tile segment, so the accumulator just stays where it is).
+          pending_acc = b;
+        } else {
+          cluster_send(d_tmem, c, n_local);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
       } else {
         // Partial tile: park the fp32 sums, then whoever completes the tile reduces.
         const int c_first = owner_of(static_cast<long long>(tile) * U, TU, G);
@@ -628,6 +645,17 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       bias4[0] = bf16lo_f32(bb.x); bias4[1] = bf16hi_f32(bb.x);
       bias4[2] = bf16lo_f32(bb.y); bias4[3] = bf16hi_f32(bb.y);
     }
+    if (p.recv_alias) {
+      // Every CTA of the cluster is past its main loop after this barrier: nothing reads or
+      // writes the rings any more, so the receive buffers that lie over them may be filled.
+      cluster_sync_all();
+      if (pending_acc >= 0) {
+        tc_fence_after();
+        cluster_send(tmem_addr(tmem0 + pending_acc * p.NU, 32 * (warp & 3), 0), lane & 3,
+                     32 * (warp & 3) + 4 * (lane >> 2));
+        tc_fence_before();
+      }
+    }
     cluster_sync_all();
     pdl_wait();
     if (n < p.N) {
@@ -753,7 +781,7 @@ static bool pdl_enabled() {
 
 struct Plan {
   int NU, planes, rows, units_per_tile, tiles, tiles_n, total_units, stages, w_stages, x_stage_bytes, ctas,
-      max_slots, nacc, recv_bytes, recv_off;
+      max_slots, nacc, recv_bytes, recv_off, recv_alias;
   size_t smem_bytes;
 };
 
@@ -782,16 +810,24 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   pl.recv_bytes = (blocks == 1 && pl.tiles * 2 <= budget_ctas && pl.units_per_tile >= 2)
                       ? (pl.NU + 8) * kTileN * 4 : 0;
   int w_stages = (kSmemBudget - pl.recv_bytes - kAStages * pl.x_stage_bytes) / kWStage;
+  pl.recv_alias = 0;
   if (pl.recv_bytes > 0 && w_stages < 2 * kAStages) {
-    // not enough room for a useful weight ring next to the receive buffers: no cluster split
-    pl.recv_bytes = 0;
+    // Not enough room for a useful weight ring next to the receive buffers (more than 96
+    // tokens): let them lie over the rings instead.  The partial rows are then sent after
+    // a cluster barrier at the end of the main loop, when the rings are idle.
     w_stages = (kSmemBudget - kAStages * pl.x_stage_bytes) / kWStage;
+    pl.recv_alias = 1;
   }
   w_stages = (w_stages / kAStages) * kAStages;
   if (w_stages > kMaxWStages) w_stages = kMaxWStages;
   pl.w_stages = w_stages;
-  pl.recv_off = pl.w_stages * kWStage + pl.stages * pl.x_stage_bytes;
-  pl.smem_bytes = static_cast<size_t>(pl.recv_off) + pl.recv_bytes + 1024;
+  const int rings = pl.w_stages * kWStage + pl.stages * pl.x_stage_bytes;
+  if (pl.recv_alias && pl.recv_bytes > rings) {  // does not fit there either: no cluster split
+    pl.recv_alias = 0;
+    pl.recv_bytes = 0;
+  }
+  pl.recv_off = pl.recv_alias ? 0 : rings;
+  pl.smem_bytes = static_cast<size_t>(rings) + (pl.recv_alias ? 0 : pl.recv_bytes) + 1024;
   // Grid: `budget` CTAs at most (all SMs unless the caller caps it, e.g. to run several
   // GEMMs side by side).
   const int budget = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
@@ -962,6 +998,7 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   }
   p.cluster = cluster;
   p.recv_off = pl.recv_off;
+  p.recv_alias = cluster > 1 ? pl.recv_alias : 0;
   p.rows_per = (M + cluster - 1) / cluster;
   p.rows_inv = (65536 + p.rows_per - 1) / p.rows_per;
 

@@ -219,7 +219,9 @@ def test_one_block_layer_set_matches_oracle_chain(d, oracle):
     (64, 3072, 3072, 8, 60, "cap that still allows a cluster of 2 per tile"),
     (83, 3072, 3072, 4, 0, "24 tiles: cluster split with the DSMEM reduce"),
     (83, 14336, 3072, 4, 0, "row-parallel shape, 112 units per tile, cluster split"),
-    (128, 3072, 3072, 4, 0, "128 tokens: no room for cluster buffers, one CTA per tile"),
+    (128, 3072, 3072, 4, 0, "128 tokens: cluster split, receive buffers laid over the idle rings"),
+    (100, 14336, 3072, 8, 0, "100 tokens, long K, int8: cluster split with aliased receive buffers"),
+    (97, 3072, 3072, 4, 40, "aliased receive buffers under a CTA cap"),
     (83, 3072, 14336, 4, 0, "112 tiles: one CTA per tile"),
 ])
 def test_launch_regimes(m, k, n, nbits, max_ctas, why, d, oracle):
