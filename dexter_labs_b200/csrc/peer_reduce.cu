@@ -174,7 +174,7 @@ int dxb_peer_allreduce(const void* partial, void* out, int64_t elems, void* cons
   P.rank = rank;
   P.world = world;
   static const int blocks = [] {
-    const char* e = getenv("DXB_PEER_BLOCKS");
+    const char* e = getenv("DEXTER_B200_PEER_BLOCKS");
     const int v = e ? atoi(e) : kPeerBlocks;
     return (v >= 1 && v <= kPeerBlocks) ? v : kPeerBlocks;
   }();
