@@ -512,14 +512,16 @@ def run_ours(args) -> int:
 
     # One GPU only: the same linears with self q/k/v and cross k/v each issued as one
     # N-concatenated launch (same arithmetic per column, but another K-split order, so equal
-    # only up to fp32 summation order; 7 launches per block instead of 10), as an extra.
+    # only up to fp32 summation order; 7 launches per block instead of 10; the cross k/v launch
+    # on a side stream next to self q/k/v), as an extra.
     # With more than one rank the main arm above already is that fused schedule.
     fused_ms, fused_same, fused_launches = None, None, None
     if world == 1:
         try:
             fused = tp.LayerSet(dim=ls.dim, ffn_dim=ls.ffn_dim, blocks=ls.blocks, rank=rank, world=world,
                                 bits=ls.bits, group_size=ls.group_size, collective=ls.collective,
-                                fuse_qkv=True, layers=[tp.LayerSet._fuse(r) for r in ls.layers])
+                                fuse_qkv=True, concurrent=True,
+                                layers=[tp.LayerSet._fuse(r) for r in ls.layers])
             fused_launches = fused.num_gemms
             yf = fused.forward(x, ctx)
             torch.cuda.synchronize()

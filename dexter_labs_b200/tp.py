@@ -376,8 +376,11 @@ class LayerSet:
         return x
 
     def _block_forward_fused_overlapped(self, blk: int, x: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
-        """More than one rank, q/k/v fused: seven launches per block, and the fused cross k/v
-        launch (context only) runs on a side stream while self o's collective is in flight."""
+        """q/k/v fused (seven launches per block) with the fused cross k/v launch, which only
+        needs the context, on a side stream.  One rank: it starts with the block, next to
+        self q/k/v, each of the two capped to its share of the SMs.  More ranks: it is held
+        back until self o's GEMM has been issued and runs while that GEMM's collective is in
+        flight on the main stream."""
         L = {l.name: l for l in self.layers[blk]}
         g = self.gemm
         cur = torch.cuda.current_stream()
@@ -385,12 +388,22 @@ class LayerSet:
             self._side = [torch.cuda.Stream() for _ in range(4)]
             self._sms = torch.cuda.get_device_properties(x.device).multi_processor_count
         side = self._side[0]
-        qkv = g(x, L["self_qkv"].weight)
-        v = qkv[:, 2 * (qkv.shape[1] // 3):]
-        partial = g(self._row_input(v, L["self_o"]), L["self_o"].weight)
-        side.wait_stream(cur)  # after self o's GEMM, alongside its collective
-        with torch.cuda.stream(side):
-            kv = g(ctx, L["cross_kv"].weight, max(self._sms // 2, 1))
+        if self.world == 1:
+            kv_tiles = -(-L["cross_kv"].weight.qweight.shape[1] // 128)
+            kv_share = max(min(kv_tiles, self._sms // 3), 1)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                kv = g(ctx, L["cross_kv"].weight, kv_share)
+            qkv = g(x, L["self_qkv"].weight, self._sms - kv_share)
+            v = qkv[:, 2 * (qkv.shape[1] // 3):]
+            partial = g(self._row_input(v, L["self_o"]), L["self_o"].weight)
+        else:
+            qkv = g(x, L["self_qkv"].weight)
+            v = qkv[:, 2 * (qkv.shape[1] // 3):]
+            partial = g(self._row_input(v, L["self_o"]), L["self_o"].weight)
+            side.wait_stream(cur)  # after self o's GEMM, alongside its collective
+            with torch.cuda.stream(side):
+                kv = g(ctx, L["cross_kv"].weight, max(self._sms // 2, 1))
         x = self._reduce(partial)
         g(x, L["cross_q"].weight)
         cur.wait_stream(side)
@@ -404,7 +417,7 @@ class LayerSet:
         """x, ctx: ``[M, dim]`` replicated on every rank; returns the new replicated x."""
         if self.concurrent and not self.fuse_qkv and x.is_cuda:
             return self._block_forward_concurrent(blk, x, ctx)
-        if self.concurrent and self.fuse_qkv and self.world > 1 and x.is_cuda:
+        if self.concurrent and self.fuse_qkv and x.is_cuda:
             return self._block_forward_fused_overlapped(blk, x, ctx)
         L = {l.name: l for l in self.layers[blk]}
         g = self.gemm
