@@ -586,7 +586,7 @@ def run_ours(args) -> int:
     tensor_peak = peaks["tflops_sustained"] if sustained else peaks["tflops"]
     t_mma_ms = set_flops / world / (tensor_peak * 1e9)
     roofline_ms = max(t_mem_ms, t_mma_ms)
-    # dominant kernel: wq_gemm_tc<4,false>; per-launch averages over the pass (per rank)
+    # dominant kernel: wq_gemm_tc<4,false,false> (int4, symmetric, one token block); per-launch averages over the pass (per rank)
     us_per_launch = ms_per_step * 1e3 / launches_per_step
     flops_per_launch = set_flops / world / launches_per_step
     bytes_per_launch = set_bytes / world / launches_per_step
@@ -607,7 +607,7 @@ def run_ours(args) -> int:
         "gpu_launches": (launches_per_step + (3 * ls.blocks if ls._peer is not None else 0)) * args.steps,
         "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
                      "frac": achieved / peak, "traffic": bytes_per_launch * DRAM_OVER_ALGORITHMIC,
-                     "kernel": "wq_gemm_tc<4,false>", "peak_source": f"{peaks['source']} ({'sustained' if sustained else 'burst'})",
+                     "kernel": "wq_gemm_tc<4,false,false>", "peak_source": f"{peaks['source']} ({'sustained' if sustained else 'burst'})",
                      "algorithmic_bytes_per_launch": bytes_per_launch,
                      "algorithmic_flops_per_launch": flops_per_launch,
                      "us_per_launch": us_per_launch,
