@@ -119,6 +119,12 @@ def _tp_worker(rank, world, port, collective, results):
         ctx = torch.randn(7, 256).to(torch.bfloat16)
         y = ls.forward(x, ctx)
         results[rank] = y.float().numpy()
+        # Without CUDA there is no peer-mapped memory: the set must say so on every rank and
+        # keep summing through the process group.
+        assert ls.enable_peer_reduce(7, "cpu") is False
+        assert ls.collective == "all_reduce" and ls._peer is None
+        y2 = ls.forward(x, ctx)
+        results[rank + world] = y2.float().numpy()
     finally:
         dist.destroy_process_group()
 
@@ -145,6 +151,9 @@ def test_two_rank_layer_set_matches_single_rank(collective, b200_lib, oracle):
         # partial sums are rounded to bf16 before the cross-rank sum: 1e-2 per the stated tolerance
         assert err < 1e-2, (rank, err)
     assert np.array_equal(results[0], results[1])  # every rank ends with the same replicated x
+    for rank in range(world):  # after the refused peer set-up: all-reduce, same tolerance
+        err = np.abs(results[rank + world] - want).max() / max(np.abs(want).max(), 1e-6)
+        assert err < 1e-2, (rank, err)
 
 
 def test_layer_set_accounting(b200_lib):
