@@ -145,7 +145,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   // Cluster mode: send this CTA's fp32 partial rows from accumulator `d_tmem` (already
   // offset to the calling warp's lane quadrant) to their owners' receive buffers.
-  auto cluster_send = [&](uint32_t d_tmem, int c, int n_local) {
+  auto cluster_send = [&](uint32_t d_tmem, int c, int n_local, int m_rows) {
     const uint32_t recv0 = smem0 + static_cast<uint32_t>(p.recv_off);
     for (int c0 = 0; c0 < p.NU; c0 += 16) {
       uint32_t ra[8], rb[8];
@@ -155,7 +155,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
       for (int rep = 0; rep < 4; ++rep) {
         const int m = c0 + 4 * rep + c;
-        if (m < p.M) {
+        if (m < m_rows) {
           const int owner = (m * p.rows_inv) >> 16;
           const int row = crank * p.rows_per + (m - owner * p.rows_per);
           st_dsmem_b32x4(dsmem_addr(recv0 + static_cast<uint32_t>(row * kTileN + n_local) * 4u, owner),
@@ -372,7 +372,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           // has exactly this one tile segment, so the accumulator just stays where it is).
           pending_acc = b;
         } else {
-          cluster_send(d_tmem, c, n_local);
+          cluster_send(d_tmem, c, n_local, m_rows);
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
@@ -627,18 +627,20 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   tc_fence_before();
   __syncthreads();
   if (C > 1) {
-    // After this barrier every partial row of this CTA's share has arrived in its receive
-    // buffers: sum them in rank order (deterministic), add the bias, write bf16.  Nothing
-    // remote is touched any more, so CTAs leave independently.
+    // The cluster's tile: token block and column tile.
+    const int tblock = MULTI ? ctile / p.tiles_n : 0;
+    const int ntile = ctile - tblock * p.tiles_n;
+    const int row0 = tblock * 128;
+    const int m_rows = MULTI ? ((p.M - row0) < 128 ? (p.M - row0) : 128) : p.M;
     const int m_lo = crank * p.rows_per;
-    const int m_hi = (m_lo + p.rows_per) < p.M ? (m_lo + p.rows_per) : p.M;
+    const int m_hi = (m_lo + p.rows_per) < m_rows ? (m_lo + p.rows_per) : m_rows;
     const uint32_t recv0 = smem0 + static_cast<uint32_t>(p.recv_off);
     const uint32_t src_stride = static_cast<uint32_t>(p.rows_per * kTileN) * 4u;
     const bool has_bias = p.bias != nullptr;
     // Every item of one thread has the same four columns (kThreads is a multiple of 32):
     // their bias is fetched before the barrier, off the critical path.
     const int c4 = (threadIdx.x & 31) * 4;
-    const int n = ctile * kTileN + c4;
+    const int n = ntile * kTileN + c4;
     float bias4[4] = {0.f, 0.f, 0.f, 0.f};
     if (has_bias && n < p.N) {
       const uint2 bb = __ldg(reinterpret_cast<const uint2*>(p.bias + n));
@@ -652,10 +654,13 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       if (pending_acc >= 0) {
         tc_fence_after();
         cluster_send(tmem_addr(tmem0 + pending_acc * p.NU, 32 * (warp & 3), 0), lane & 3,
-                     32 * (warp & 3) + 4 * (lane >> 2));
+                     32 * (warp & 3) + 4 * (lane >> 2), m_rows);
         tc_fence_before();
       }
     }
+    // After this barrier every partial row of this CTA's share has arrived in its receive
+    // buffers: sum them in rank order (deterministic), add the bias, write bf16.  Nothing
+    // remote is touched any more, so CTAs leave independently.
     cluster_sync_all();
     pdl_wait();
     if (n < p.N) {
@@ -680,7 +685,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           pk.x = cvt_bf16x2(acc.y, acc.x);
           pk.y = cvt_bf16x2(acc.w, acc.z);
         }
-        *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m_lo + j) * p.ldo + n) = pk;
+        *reinterpret_cast<uint2*>(p.out + static_cast<long long>(row0 + m_lo + j) * p.ldo + n) = pk;
       }
     }
   }
@@ -807,8 +812,7 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   // Launches that may split tiles over a cluster keep room for its receive buffers
   // (at most NU + 8 token rows of 128 fp32) behind the two rings.
   const int budget_ctas = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
-  pl.recv_bytes = (blocks == 1 && pl.tiles * 2 <= budget_ctas && pl.units_per_tile >= 2)
-                      ? (pl.NU + 8) * kTileN * 4 : 0;
+  pl.recv_bytes = (pl.tiles * 2 <= budget_ctas && pl.units_per_tile >= 2) ? (pl.NU + 8) * kTileN * 4 : 0;
   int w_stages = (kSmemBudget - pl.recv_bytes - kAStages * pl.x_stage_bytes) / kWStage;
   pl.recv_alias = 0;
   if (pl.recv_bytes > 0 && w_stages < 2 * kAStages) {
@@ -999,7 +1003,7 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   p.cluster = cluster;
   p.recv_off = pl.recv_off;
   p.recv_alias = cluster > 1 ? pl.recv_alias : 0;
-  p.rows_per = (M + cluster - 1) / cluster;
+  p.rows_per = ((M > 128 ? 128 : M) + cluster - 1) / cluster;  // token rows of one block per CTA
   p.rows_inv = (65536 + p.rows_per - 1) / p.rows_per;
 
   cudaLaunchConfig_t cfg = {};
