@@ -83,8 +83,12 @@ template <int BITS, bool HAS_ZERO, bool MULTI>
 __global__ void __launch_bounds__(kThreads, 1)
 wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_x,
            const WqParams p) {
-  constexpr int PLANES = BITS == 4 ? 2 : 1;
+  // A unit is 128 logical k of 128 weight columns in two planes of 64: for int4 the low and the
+  // high nibbles of 64 packed rows (k and k + K/2), for int8 two consecutive blocks of 64 rows.
+  constexpr int PLANES = 2;
   constexpr int A_STAGE_COLS = PLANES * 32;
+  constexpr int UNIT_ROWS = BITS == 4 ? 64 : 128;   // packed rows per unit
+  constexpr int W_STAGE = UNIT_ROWS * kTileN;       // bytes of one packed-weight stage
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[kNumBars];
@@ -95,7 +99,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t w_ring = smem0;
-  const uint32_t x_ring = smem0 + p.w_stages * kWStage;
+  const uint32_t x_ring = smem0 + p.w_stages * W_STAGE;
   const uint32_t bar0 = smem_u32(bars);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -184,8 +188,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (!ok) break;
         if (elect_one()) {
           const uint32_t fw = bar0 + 8 * (kBarFullW + s);
-          mbar_expect_tx(fw, kQBytes);
-          tma_load_2d(w_ring + s * kWStage, &tm_q, fw, (MULTI ? ntile : tile) * kTileN, ku * kUnitRows);
+          mbar_expect_tx(fw, W_STAGE);
+          tma_load_2d(w_ring + s * W_STAGE, &tm_q, fw, (MULTI ? ntile : tile) * kTileN, ku * UNIT_ROWS);
         }
         __syncwarp();
         ++issued;
@@ -219,10 +223,12 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         if (elect_one()) {
           const uint32_t rb = bar0 + 8 * (kBarReady + t);
           mbar_expect_tx(rb, x_bytes);
-          if (BITS == 4)
-            tma_load_3d(x_ring + t * p.x_stage_bytes, &tm_x, rb, ku * kUnitRows, row0, 0);
-          else
-            tma_load_2d(x_ring + t * p.x_stage_bytes, &tm_x, rb, ku * kUnitRows, row0);
+          if (BITS == 4) {
+            tma_load_3d(x_ring + t * p.x_stage_bytes, &tm_x, rb, ku * 64, row0, 0);
+          } else {  // two k-blocks of 64, one per plane
+            tma_load_2d(x_ring + t * p.x_stage_bytes, &tm_x, rb, ku * 128, row0);
+            tma_load_2d(x_ring + t * p.x_stage_bytes + (x_bytes >> 1), &tm_x, rb, ku * 128 + 64, row0);
+          }
         }
         __syncwarp();
         ++issued;
@@ -499,8 +505,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const uint32_t off1 = (2 * c + 1) * 128 + ((chunk ^ (2 * c + 1)) << 4) + 4 * (g & 3);
     const uint32_t lane_base = 32 * q;
     const int n_local = 32 * q + 4 * g;
-    const int group_units = p.group / kUnitRows;
-    const int half_units = p.half_k / kUnitRows;
+    const int group_units = p.group / 64;   // quantisation group in planes of 64 k
+    const int half_units = p.half_k / 64;    // int4: planes between the low and the high nibbles
     const uint2* sc_ptr = reinterpret_cast<const uint2*>(p.scales);
     const uint2* zr_ptr = reinterpret_cast<const uint2*>(p.zeros);
     const uint32_t a_tmem = tmem0 + kACol0 + team * A_STAGE_COLS;
@@ -525,7 +531,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const bool in = n < p.N && tile_ < p.tiles;
 #pragma unroll
       for (int pl = 0; pl < PLANES; ++pl) {
-        const int kunit = ku_ + pl * half_units;
+        const int kunit = BITS == 4 ? ku_ + pl * half_units : 2 * ku_ + pl;  // plane of 64 k
         const int grp = p.group_shift >= 0 ? (kunit >> p.group_shift) : (kunit / group_units);
         const int idx = grp * n4_stride + (n >> 2);
         s_out[pl] = in ? __ldg(sc_ptr + idx) : make_uint2(0u, 0u);
@@ -545,15 +551,17 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       ok = mbar_wait(bar0 + 8 * (kBarFullW + s), ph, abortp);
       if (!ok) break;
       if (q == 0 && lane == 0) DX_TRACE(4, (u - u_begin));
-      const uint32_t wsrc = w_ring + s * kWStage;
+      const uint32_t wsrc = w_ring + s * W_STAGE;
       uint32_t w0[8], w1[8];
 #pragma unroll
       for (int sl = 0; sl < 8; ++sl) {
         w0[sl] = lds32(wsrc + off0 + sl * 1024);
         w1[sl] = lds32(wsrc + off1 + sl * 1024);
       }
-      __syncwarp();  // every lane has its words in registers
-      if (lane == 0) mbar_arrive(bar0 + 8 * (kBarEmptyW + s));
+      if (BITS == 4) {  // (int8 reads the second half of its stage further down)
+        __syncwarp();  // every lane has its words in registers
+        if (lane == 0) mbar_arrive(bar0 + 8 * (kBarEmptyW + s));
+      }
       ok = mbar_wait(a_empty_bar, aph ^ 1u, abortp);
       if (!ok) break;
       if (q == 0 && lane == 0) DX_TRACE(6, (u - u_begin));
@@ -587,28 +595,41 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           }
         }
       } else {
-        const float sf[4] = {bf16lo_f32(sc[0].x), bf16hi_f32(sc[0].x), bf16lo_f32(sc[0].y),
-                             bf16hi_f32(sc[0].y)};
-        float cz[4];
-        if (HAS_ZERO) {
-          cz[0] = 8388608.0f + bf16lo_f32(zr[0].x); cz[1] = 8388608.0f + bf16hi_f32(zr[0].x);
-          cz[2] = 8388608.0f + bf16lo_f32(zr[0].y); cz[3] = 8388608.0f + bf16hi_f32(zr[0].y);
-        } else {
-          cz[0] = cz[1] = cz[2] = cz[3] = 8388608.0f + 128.0f;
-        }
 #pragma unroll
-        for (int rh = 0; rh < 2; ++rh) {
-          uint32_t ra[8], rb[8];
+        for (int pl = 0; pl < 2; ++pl) {
+          if (pl == 1) {
+            // rows 64..127 of the unit; after these loads the stage can be refilled
 #pragma unroll
-          for (int sl = 0; sl < 4; ++sl) {
-            const uint32_t x0 = w0[4 * rh + sl], x1 = w1[4 * rh + sl];
-            ra[2 * sl + 0] = cvt_bf16x2(deq8(x1, 0, cz[0], sf[0]), deq8(x0, 0, cz[0], sf[0]));
-            ra[2 * sl + 1] = cvt_bf16x2(deq8(x1, 1, cz[1], sf[1]), deq8(x0, 1, cz[1], sf[1]));
-            rb[2 * sl + 0] = cvt_bf16x2(deq8(x1, 2, cz[2], sf[2]), deq8(x0, 2, cz[2], sf[2]));
-            rb[2 * sl + 1] = cvt_bf16x2(deq8(x1, 3, cz[3], sf[3]), deq8(x0, 3, cz[3], sf[3]));
+            for (int sl = 0; sl < 8; ++sl) {
+              w0[sl] = lds32(wsrc + 8192 + off0 + sl * 1024);
+              w1[sl] = lds32(wsrc + 8192 + off1 + sl * 1024);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar0 + 8 * (kBarEmptyW + s));
           }
-          tmem_st_16x128b_x4(tmem_addr(a_tmem + 16 * rh, lane_base, 0), ra);
-          tmem_st_16x128b_x4(tmem_addr(a_tmem + 16 * rh, lane_base + 16, 0), rb);
+          const float sf[4] = {bf16lo_f32(sc[pl].x), bf16hi_f32(sc[pl].x), bf16lo_f32(sc[pl].y),
+                               bf16hi_f32(sc[pl].y)};
+          float cz[4];
+          if (HAS_ZERO) {
+            cz[0] = 8388608.0f + bf16lo_f32(zr[pl].x); cz[1] = 8388608.0f + bf16hi_f32(zr[pl].x);
+            cz[2] = 8388608.0f + bf16lo_f32(zr[pl].y); cz[3] = 8388608.0f + bf16hi_f32(zr[pl].y);
+          } else {
+            cz[0] = cz[1] = cz[2] = cz[3] = 8388608.0f + 128.0f;
+          }
+#pragma unroll
+          for (int rh = 0; rh < 2; ++rh) {
+            uint32_t ra[8], rb[8];
+#pragma unroll
+            for (int sl = 0; sl < 4; ++sl) {
+              const uint32_t x0 = w0[4 * rh + sl], x1 = w1[4 * rh + sl];
+              ra[2 * sl + 0] = cvt_bf16x2(deq8(x1, 0, cz[0], sf[0]), deq8(x0, 0, cz[0], sf[0]));
+              ra[2 * sl + 1] = cvt_bf16x2(deq8(x1, 1, cz[1], sf[1]), deq8(x0, 1, cz[1], sf[1]));
+              rb[2 * sl + 0] = cvt_bf16x2(deq8(x1, 2, cz[2], sf[2]), deq8(x0, 2, cz[2], sf[2]));
+              rb[2 * sl + 1] = cvt_bf16x2(deq8(x1, 3, cz[3], sf[3]), deq8(x0, 3, cz[3], sf[3]));
+            }
+            tmem_st_16x128b_x4(tmem_addr(a_tmem + pl * 32 + 16 * rh, lane_base, 0), ra);
+            tmem_st_16x128b_x4(tmem_addr(a_tmem + pl * 32 + 16 * rh, lane_base + 16, 0), rb);
+          }
         }
       }
       tc_wait_st();
@@ -785,7 +806,8 @@ static bool pdl_enabled() {
 }
 
 struct Plan {
-  int NU, planes, rows, units_per_tile, tiles, tiles_n, total_units, stages, w_stages, x_stage_bytes, ctas,
+  int NU, planes, rows, unit_rows, w_stage_bytes, units_per_tile, tiles, tiles_n, total_units, stages,
+      w_stages, x_stage_bytes, ctas,
       max_slots, nacc, recv_bytes, recv_off, recv_alias;
   size_t smem_bytes;
 };
@@ -797,9 +819,12 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   // its own, so one launch covers all of them and every SM stays busy.
   const int blocks = (M + 127) / 128;
   pl.NU = blocks > 1 ? 128 : ((M + 15) / 16) * 16;
-  pl.planes = bits == 4 ? 2 : 1;
+  // A unit is 128 logical k in two planes of 64: 64 packed rows of int4, 128 rows of int8.
+  pl.planes = 2;
   pl.rows = bits == 4 ? K / 2 : K;
-  pl.units_per_tile = pl.rows / kUnitRows;
+  pl.unit_rows = bits == 4 ? 64 : 128;
+  pl.w_stage_bytes = pl.unit_rows * kTileN;
+  pl.units_per_tile = pl.rows / pl.unit_rows;
   pl.tiles_n = (N + kTileN - 1) / kTileN;
   pl.tiles = pl.tiles_n * blocks;
   pl.total_units = pl.units_per_tile * pl.tiles;
@@ -813,19 +838,19 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   // (at most NU + 8 token rows of 128 fp32) behind the two rings.
   const int budget_ctas = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
   pl.recv_bytes = (pl.tiles * 2 <= budget_ctas && pl.units_per_tile >= 2) ? (pl.NU + 8) * kTileN * 4 : 0;
-  int w_stages = (kSmemBudget - pl.recv_bytes - kAStages * pl.x_stage_bytes) / kWStage;
+  int w_stages = (kSmemBudget - pl.recv_bytes - kAStages * pl.x_stage_bytes) / pl.w_stage_bytes;
   pl.recv_alias = 0;
-  if (pl.recv_bytes > 0 && w_stages < 2 * kAStages) {
+  if (pl.recv_bytes > 0 && (w_stages / kAStages) * kAStages * pl.w_stage_bytes < 2 * kAStages * kWStage) {
     // Not enough room for a useful weight ring next to the receive buffers (more than 96
     // tokens): let them lie over the rings instead.  The partial rows are then sent after
     // a cluster barrier at the end of the main loop, when the rings are idle.
-    w_stages = (kSmemBudget - kAStages * pl.x_stage_bytes) / kWStage;
+    w_stages = (kSmemBudget - kAStages * pl.x_stage_bytes) / pl.w_stage_bytes;
     pl.recv_alias = 1;
   }
   w_stages = (w_stages / kAStages) * kAStages;
   if (w_stages > kMaxWStages) w_stages = kMaxWStages;
   pl.w_stages = w_stages;
-  const int rings = pl.w_stages * kWStage + pl.stages * pl.x_stage_bytes;
+  const int rings = pl.w_stages * pl.w_stage_bytes + pl.stages * pl.x_stage_bytes;
   if (pl.recv_alias && pl.recv_bytes > rings) {  // does not fit there either: no cluster split
     pl.recv_alias = 0;
     pl.recv_bytes = 0;
@@ -844,8 +869,8 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   const int whole_ctas = (pl.tiles + rounds - 1) / rounds;
   const long long whole_units = static_cast<long long>(rounds) * pl.units_per_tile;
   // measured cost of the global fix-up in units: ~16 at <= 96 tokens, ~28 with 128-token
-  // accumulators (larger partial tiles); half as much again for int8, whose units are shorter
-  const int fixup_units = (pl.NU > 96 ? 28 : 16) * (bits == 8 ? 3 : 2) / 2;
+  // accumulators (larger partial tiles)
+  const int fixup_units = pl.NU > 96 ? 28 : 16;
   const long long split_units = (pl.total_units + budget - 1) / budget + fixup_units;
   int ctas = (pl.tiles % whole_ctas == 0 && whole_units <= split_units) ? whole_ctas : budget;
   if (ctas > pl.total_units) ctas = pl.total_units;
@@ -865,6 +890,11 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
 // The counter block has one fixed size so that calls with different tile counts
 // never let one call's partial sums land on another call's counters.
 static size_t counters_bytes(int) { return static_cast<size_t>(kMaxTiles) * 4; }
+
+// Shapes wq_gemm_tc takes: those of tc_supported, and for int8 whole units of 128 rows.
+static bool gemm_tc_supported(int M, int N, int K, int group, int bits) {
+  return tc_supported(M, N, K, group, bits) && (bits != 8 || K % 128 == 0);
+}
 
 // Workspace the tensor-core launch of this problem needs (status, counters, partial sums).
 static size_t plan_workspace_bytes(int M, int N, int K, int bits, int max_ctas) {
@@ -892,7 +922,7 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(pl.rows)};
     const uint64_t strides[1] = {static_cast<uint64_t>(N)};
-    const uint32_t box[2] = {kTileN, kUnitRows};
+    const uint32_t box[2] = {kTileN, static_cast<uint32_t>(pl.unit_rows)};
     ok = make_map(&tq, qw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, dims, strides, box,
                   CU_TENSOR_MAP_SWIZZLE_128B);
   }
@@ -1098,7 +1128,7 @@ int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const
   // More than 128 tokens: one launch over all token blocks when the workspace holds the
   // partial sums of that plan (dxb_workspace_bytes asks for it); a smaller workspace still
   // works, block by block.
-  if (M > 128 && aligned && tc_supported(M, N, K, group_size, bits) &&
+  if (M > 128 && aligned && gemm_tc_supported(M, N, K, group_size, bits) &&
       workspace_bytes >= plan_workspace_bytes(M, N, K, bits, max_ctas))
     return launch(static_cast<const char*>(x), static_cast<char*>(out), M);
   // Token blocks of at most 128 rows per launch (the UMMA N of one accumulator); 96 when the
@@ -1110,7 +1140,7 @@ int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const
     const int mc = (M - m0) < chunk ? (M - m0) : chunk;
     const char* xc = static_cast<const char*>(x) + static_cast<long long>(m0) * ldx * 2;
     char* oc = static_cast<char*>(out) + static_cast<long long>(m0) * ldo * 2;
-    if (aligned && tc_supported(mc, N, K, group_size, bits)) {
+    if (aligned && gemm_tc_supported(mc, N, K, group_size, bits)) {
       rc = launch(xc, oc, mc);
     } else {
       rc = bits == 4 ? launch_simt<4>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
@@ -1165,7 +1195,7 @@ int dxb_wq_gemm_static(int bits, const void* x, int64_t ldx, const void* qweight
   // one-launch plan when the array holds it and goes block by block otherwise.
   {
     const int rows = bits == 4 ? K / 2 : K;
-    if (rows >= kUnitRows &&
+    if (rows >= (bits == 4 ? 64 : 128) &&
         (plan_workspace_bytes(M <= 128 ? M : 128, N, K, bits, 0) > kStaticScratchBytes ||
          (M > 128 && plan_workspace_bytes(96, N, K, bits, 0) > kStaticScratchBytes)))
       return DXB_ERR_SCRATCH_LIMIT;
@@ -1200,7 +1230,7 @@ size_t dxb_workspace_bytes(int M, int N, int K, int bits) {
   using namespace dx;
   if (M <= 0 || N <= 0 || K <= 0 || (bits != 4 && bits != 8)) return kStatusBytes;
   const int rows = bits == 4 ? K / 2 : K;
-  if (rows < kUnitRows) return kStatusBytes;
+  if (rows < (bits == 4 ? 64 : 128)) return kStatusBytes;
   // Up to 128 tokens: that launch.  More: the larger of the one-launch plan over all token
   // blocks and the plan of a single block (used when the caller's workspace is smaller).
   size_t one_block = plan_workspace_bytes(M <= 128 ? M : 128, N, K, bits, 0);
@@ -1238,7 +1268,7 @@ int dxb_dequantize(const void* qweight, const void* scales, const void* zeros, v
 
 int dxb_uses_tensor_cores(int M, int N, int K, int group_size, int bits) {
   const int mc = M <= 128 ? M : 128;
-  return dx::tc_supported(mc, N, K, group_size, bits) ? 1 : 0;
+  return dx::gemm_tc_supported(mc, N, K, group_size, bits) ? 1 : 0;
 }
 
 int dxb_read_status(void* workspace, void* cuda_stream) {
