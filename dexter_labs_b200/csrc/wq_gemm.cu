@@ -12,7 +12,7 @@
 // Tensor-core kernel (wq_gemm_tc): the weight tile is the 128-row UMMA "M"
 // operand and the tokens are the UMMA "N" (swap-AB), so M = 83 tokens costs a
 // 96-wide MMA instead of a 128-row one.  24 warps per CTA, one CTA per SM; per unit
-// of 64 packed rows x 128 columns:
+// of 128 logical k x 128 columns (64 packed rows of int4, 128 rows of int8):
 //   warps 0, 3   TMA producers: packed bytes of alternate units land in a
 //                shared-memory ring (128 B swizzle).
 //   warp 2       TMA producer: the matching activation k-slices (both nibble planes
