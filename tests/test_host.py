@@ -212,3 +212,29 @@ def test_strerror_and_argument_checks(b200_lib):
     assert b200_lib.dxb_uses_tensor_cores(83, 200, 3072, 128, 4) == 0   # N % 16
     assert b200_lib.dxb_uses_tensor_cores(83, 256, 256, 32, 4) == 0     # group < 64 rows
     assert b200_lib.dxb_uses_tensor_cores(913, 3072, 3072, 128, 4) == 1  # token blocks of 128
+    assert b200_lib.dxb_uses_tensor_cores(83, 3072, 3072, 3072, 8) == 1   # int8: units of 128 rows
+    assert b200_lib.dxb_uses_tensor_cores(83, 3072, 192, 64, 8) == 0      # int8 with K % 128 != 0
+
+
+def test_chain_and_peer_entry_points_check_their_arguments(b200_lib):
+    """Argument checks of the list and all-reduce entry points return before any launch."""
+    from dexter_labs_b200 import _lib
+
+    assert ctypes.sizeof(_lib.ChainItem) == 88  # 8 pointers/strides of 8 bytes + 5 ints, padded
+    items = (_lib.ChainItem * 1)()
+    assert b200_lib.dxb_wq_gemm_chain(3, items, 1, None, 0, 0, None) == -1     # bits
+    assert b200_lib.dxb_wq_gemm_chain(4, None, 1, None, 0, 0, None) == -2      # no items
+    assert b200_lib.dxb_wq_gemm_chain(4, items, 0, None, 0, 0, None) == -4     # empty list
+    assert b200_lib.dxb_wq_gemm_chain(4, items, _lib.DXB_CHAIN_MAX + 1, None, 0, 0, None) == -4
+    assert b200_lib.dxb_chain_workspace_bytes(4, items, 0, 0) == 0
+    # peer all-reduce: region size is plain arithmetic; bad ranks and sizes are refused
+    one = b200_lib.dxb_peer_allreduce_bytes(2, 1024)
+    assert one > 2 * 2 * 1024 * 2 and b200_lib.dxb_peer_allreduce_bytes(8, 1024) > one
+    assert b200_lib.dxb_peer_allreduce_bytes(9, 1024) == 0
+    assert b200_lib.dxb_peer_allreduce_bytes(2, 0) == 0
+    vp = ctypes.c_void_p
+    regions = (vp * 2)(vp(256), vp(512))
+    assert b200_lib.dxb_peer_allreduce(None, vp(16), 8, regions, 8, 0, 2, None, None) == -2
+    assert b200_lib.dxb_peer_allreduce(vp(16), vp(16), 8, regions, 8, 2, 2, None, None) == -3   # rank
+    assert b200_lib.dxb_peer_allreduce(vp(16), vp(16), 12, regions, 16, 0, 2, None, None) == -3  # % 8
+    assert b200_lib.dxb_peer_allreduce(vp(16), vp(16), 16, regions, 8, 0, 2, None, None) == -3   # capacity
