@@ -18,10 +18,10 @@
 namespace dx {
 // ------------------------------------------------------------------ constants
 constexpr int kTileN = 128;      // weight columns per tile (UMMA M)
-constexpr int kUnitRows = 64;    // packed rows per pipeline unit
-constexpr int kQBytes = kTileN * kUnitRows;  // 8192
+constexpr int kUnitRows = 64;    // packed rows per plane of a unit (one plane = 64 logical k);
+                                 // the chain kernel's units are one such block of rows
+constexpr int kQBytes = kTileN * kUnitRows;  // 8192: bytes of 64 packed rows of a tile
 constexpr int kWStage = kQBytes;
-constexpr int kMaxStages = 8;    // activation ring
 constexpr int kMaxWStages = 16;  // packed-weight ring; always a multiple of kAStages
 constexpr int kAStages = 4;      // dequantised-tile ring in TMEM
 constexpr int kACol0 = 256;      // TMEM column where that ring starts
