@@ -18,25 +18,31 @@ ERRORS = {
     -8: "DXB_ERR_KERNEL_TIMEOUT", -9: "DXB_ERR_SCRATCH_LIMIT",
 }
 
-DXB_CHAIN_MAX = 32
+LAYOUT_DEXTER, LAYOUT_B200 = 0, 1
+EPILOGUE_NONE, EPILOGUE_GELU_TANH = 0, 1
 
 
-class ChainItem(ctypes.Structure):
-    """``dxb_chain_item`` of include/dexter_b200.h."""
-    _fields_ = [("x", c_void_p), ("ldx", c_int64), ("qweight", c_void_p), ("scales", c_void_p),
-                ("zeros", c_void_p), ("bias", c_void_p), ("out", c_void_p), ("ldo", c_int64),
-                ("M", c_int), ("N", c_int), ("K", c_int), ("group_size", c_int),
-                ("depends_on", c_int)]
+class GemmOpts(ctypes.Structure):
+    """``dxb_gemm_opts`` of include/dexter_b200.h."""
+    _fields_ = [("weight_layout", c_int), ("epilogue", c_int), ("max_ctas", c_int),
+                ("peer_world", c_int), ("peer_rank", c_int),
+                ("peer_regions", ctypes.POINTER(c_void_p)), ("peer_capacity_elems", c_int64)]
 
 
 # name -> (restype, argtypes); one entry per symbol declared in include/dexter_b200.h
 SIGNATURES = {
+    "dxb_wq_gemm_ex": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
+                               ctypes.POINTER(GemmOpts), c_void_p]),
+    "dxb_fused_reduce_bytes": (c_size_t, [c_int, c_int64]),
+    "dxb_relayout_w4": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "dxb_workspace_bytes_ex": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "dxb_dequantize_ex": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                  c_int, c_void_p]),
+    "dxb_set_wait_limit_ms": (None, [c_int]),
     "dxb_peer_allreduce_bytes": (c_size_t, [c_int, c_int64]),
     "dxb_peer_allreduce": (c_int, [c_void_p, c_void_p, c_int64, ctypes.POINTER(c_void_p), c_int64,
                                    c_int, c_int, c_void_p, c_void_p]),
-    "dxb_chain_workspace_bytes": (c_size_t, [c_int, ctypes.POINTER(ChainItem), c_int, c_int]),
-    "dxb_wq_gemm_chain": (c_int, [c_int, ctypes.POINTER(ChainItem), c_int, c_void_p, c_size_t,
-                                  c_int, c_void_p]),
     "dxb_wq_gemm": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_size_t,
                             c_int, c_void_p]),

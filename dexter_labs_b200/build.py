@@ -14,8 +14,7 @@ import sys
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
-SOURCES = [PKG_DIR / "csrc" / "wq_gemm.cu", PKG_DIR / "csrc" / "wq_chain.cu",
-           PKG_DIR / "csrc" / "peer_reduce.cu"]
+SOURCES = [PKG_DIR / "csrc" / "wq_gemm.cu", PKG_DIR / "csrc" / "peer_reduce.cu"]
 HEADERS = [PKG_DIR / "csrc" / "sm100_ptx.cuh", PKG_DIR / "csrc" / "wq_common.cuh", PKG_DIR.parent / "include" / "dexter_b200.h"]
 LIB_PATH = PKG_DIR / "libdexter_b200.so"
 

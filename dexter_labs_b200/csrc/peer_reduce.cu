@@ -30,6 +30,7 @@
 #include "../../include/dexter_b200.h"
 
 namespace dx {
+unsigned wait_tries();  // wq_gemm.cu: polls before a wait on a peer gives up
 
 constexpr int kPeerBlocks = 128;     // grid of every rank (must be equal on all ranks)
 constexpr int kPeerThreads = 128;    // 128 threads x <= 32 registers: a block fits beside a GEMM CTA on the same SM
@@ -45,6 +46,7 @@ struct PeerParams {
   long long vecs;                        // elems / 8
   long long capacity_vecs;               // capacity / 8
   int rank, world;
+  unsigned wait_tries;                   // polls of ~0.25 us before the wait for a peer gives up
 };
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
@@ -105,7 +107,7 @@ peer_allreduce_kernel(const __grid_constant__ PeerParams P) {
     const unsigned* flag = reinterpret_cast<const unsigned*>(mine + kPeerControlBytes) +
                            threadIdx.x * kPeerBlocks + b;
     bool ok = false;
-    for (unsigned tries = 0; tries < 4000000u; ++tries) {
+    for (unsigned tries = 0; tries < P.wait_tries; ++tries) {
       // >=: a peer may already have gone on to the next call (it cannot be further ahead)
       if (static_cast<int>(ld_acquire_sys(flag) - epoch) >= 0) { ok = true; break; }
       __nanosleep(tries < 64 ? 32 : 256);
@@ -173,6 +175,7 @@ int dxb_peer_allreduce(const void* partial, void* out, int64_t elems, void* cons
   P.capacity_vecs = capacity_elems / 8;
   P.rank = rank;
   P.world = world;
+  P.wait_tries = wait_tries();
   static const int blocks = [] {
     const char* e = getenv("DEXTER_B200_PEER_BLOCKS");
     const int v = e ? atoi(e) : kPeerBlocks;

@@ -83,48 +83,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
-// Cluster-scope variants: another CTA of the cluster arrives on a barrier in THIS CTA's
-// shared memory after writing this CTA's shared memory (st.shared::cluster).  The arrive
-// releases, the wait acquires, both at cluster scope, so those writes are visible to the
-// waiter.  `cluster_bar` is a shared::cluster address (see dsmem_addr).
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_parked_cluster(uint32_t bar, uint32_t parity,
-                                                             uint32_t hint_ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(hint_ns)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
-                                                  volatile int* abort_flag) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  for (uint32_t tries = 0; tries < kWaitTries; ++tries) {
-    if (mbar_try_wait_parked_cluster(bar, parity, kWaitHintNs)) return true;
-    if (*abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
 // --------------------------------------------------------------------- TMA --
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
@@ -139,14 +97,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
-__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const void* tmap, uint32_t bar,
-                                                 int x, int y, uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-      " [%0], [%1, {%3, %4}], [%2], %5;"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "l"(policy)
-      : "memory");
-}
 // 3-D tiled load (x innermost).
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint32_t bar, int x,
                                             int y, int z) {
@@ -156,26 +106,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-__device__ __forceinline__ void fence_proxy_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
-// Orders this thread's generic-proxy accesses (ordinary loads and stores) against
-// async-proxy accesses (TMA) to the same global or shared memory, in both directions.
-__device__ __forceinline__ void fence_proxy_async_all() {
-  asm volatile("fence.proxy.async;" ::: "memory");
-}
-
 // -------------------------------------------------- flags in global memory --
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   int v;
@@ -211,14 +141,6 @@ __device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t ran
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
   return remote;
-}
-__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t cluster_addr) {
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(cluster_addr)
-               : "memory");
-  return v;
 }
 __device__ __forceinline__ void st_dsmem_b32x4(uint32_t cluster_addr, uint32_t a, uint32_t b,
                                                uint32_t c, uint32_t d) {

@@ -2,6 +2,7 @@
 // ring constants, the bit-pattern dequantisation arithmetic, the barrier slots of
 // the warp-specialised pipeline, and the host helpers that encode TMA tensor maps.
 #pragma once
+#include <atomic>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -18,8 +19,7 @@
 namespace dx {
 // ------------------------------------------------------------------ constants
 constexpr int kTileN = 128;      // weight columns per tile (UMMA M)
-constexpr int kUnitRows = 64;    // packed rows per plane of a unit (one plane = 64 logical k);
-                                 // the chain kernel's units are one such block of rows
+constexpr int kUnitRows = 64;    // packed rows per plane of a unit (one plane = 64 logical k)
 constexpr int kQBytes = kTileN * kUnitRows;  // 8192: bytes of 64 packed rows of a tile
 constexpr int kWStage = kQBytes;
 constexpr int kMaxWStages = 16;  // packed-weight ring; always a multiple of kAStages
@@ -183,5 +183,9 @@ inline bool tc_supported(int M, int N, int K, int group, int bits) {
 }
 
 constexpr size_t kStatusBytes = 256;
+
+// Polls (of about a quarter of a microsecond) a wait on a flag written by ANOTHER GPU makes
+// before it gives up; set through dxb_set_wait_limit_ms, about a second by default.
+unsigned wait_tries();
 
 }  // namespace dx

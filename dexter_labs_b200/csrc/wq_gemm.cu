@@ -42,6 +42,91 @@ namespace dx {
 #endif
 
 
+// ---------------------------------------------------------------------------
+// Sum over tensor-parallel ranks fused into the row-parallel GEMM (dxb_gemm_opts.peer_*).
+// Every rank owns a region of peer-mapped memory with the same layout:
+//   [ control: epoch, exit count ][ arrived: tiles x 8 u32 ][ base: tiles x 8 u32 ]
+//   [ recv: 2 parities x world x capacity bf16 ]
+// Whoever finishes rows of a 128-column tile (an epilogue warp group or a cluster's owner
+// CTA) rounds its fp32 partial sums to bf16 and stores them into slot `rank` of EVERY rank's
+// receive buffer (plain 8-byte stores over NVLink, own region included), fences at system
+// scope, and adds the number of rows it delivered to arrived[tile][rank] on every rank
+// (red.release.sys).  It then waits (bounded) until arrived[tile][s] - base[tile][s] has
+// reached the tile's row count for every sender s -- rows are counted, not chunks, so ranks
+// may cut their tiles differently -- adds the world slots in rank order in fp32 (every rank
+// computes the same bits), applies bias / activation and writes bf16.  The last CTA to
+// leave adds the row count to base[][] and advances the epoch (= receive-buffer parity), so
+// a captured graph replays.  A rank can be at most one call ahead of a peer, and it then
+// writes the other parity.  Only plain peer loads/stores and system-scope fences.
+constexpr int kPeerMaxRanks = 8;
+constexpr int kFusedMaxTiles = 512;
+constexpr size_t kFusedControlBytes = 256;
+constexpr size_t kFusedCounterBytes = static_cast<size_t>(kFusedMaxTiles) * kPeerMaxRanks * sizeof(unsigned);
+constexpr size_t kFusedHeaderBytes = kFusedControlBytes + 2 * kFusedCounterBytes;
+
+struct PeerFuse {
+  unsigned char* region[kPeerMaxRanks];  // every rank's region as mapped in this process
+  long long capacity;                    // bf16 elements per receive slot (>= M * N)
+  int rank, world;
+  unsigned wait_tries;                   // polls of ~0.25 us before a wait gives up
+};
+
+__device__ __forceinline__ unsigned* fused_arrived(unsigned char* region, int tile, int sender) {
+  return reinterpret_cast<unsigned*>(region + kFusedControlBytes) + tile * kPeerMaxRanks + sender;
+}
+__device__ __forceinline__ unsigned* fused_base(unsigned char* region, int tile, int sender) {
+  return reinterpret_cast<unsigned*>(region + kFusedControlBytes + kFusedCounterBytes) +
+         tile * kPeerMaxRanks + sender;
+}
+__device__ __forceinline__ __nv_bfloat16* fused_recv(const PeerFuse& pf, int owner, unsigned parity, int sender) {
+  return reinterpret_cast<__nv_bfloat16*>(pf.region[owner] + kFusedHeaderBytes) +
+         (static_cast<long long>(parity) * pf.world + sender) * pf.capacity;
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned* ptr, unsigned v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* ptr) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+// Deliver four consecutive columns of one token row to slot `rank` of every rank.
+__device__ __forceinline__ void fused_push4(const PeerFuse& pf, unsigned parity, long long elem,
+                                            float f0, float f1, float f2, float f3) {
+  const uint2 pk = make_uint2(cvt_bf16x2(f1, f0), cvt_bf16x2(f3, f2));
+  for (int r = 0; r < pf.world; ++r)
+    *reinterpret_cast<uint2*>(fused_recv(pf, r, parity, pf.rank) + elem) = pk;
+}
+// Tell every rank that `rows` more rows of `tile` from this rank are in place (one thread
+// per destination rank; the caller has fenced and synchronised the storing threads).
+__device__ __forceinline__ void fused_signal(const PeerFuse& pf, int tile, int dest, unsigned rows) {
+  red_release_sys_add(fused_arrived(pf.region[dest], tile, pf.rank), rows);
+}
+// One thread per sender: bounded wait until that sender's rows of `tile` have all arrived.
+__device__ __forceinline__ bool fused_wait(const PeerFuse& pf, int tile, int sender, unsigned rows,
+                                           volatile int* abort_flag) {
+  unsigned char* mine = pf.region[pf.rank];
+  const unsigned base = __ldcg(fused_base(mine, tile, sender));
+  const unsigned* arrived = fused_arrived(mine, tile, sender);
+  for (unsigned tries = 0; tries < pf.wait_tries; ++tries) {
+    if (static_cast<int>(ld_acquire_sys_u32(arrived) - base - rows) >= 0) return true;
+    if (*abort_flag) return false;
+    __nanosleep(tries < 64 ? 32 : 256);
+  }
+  *abort_flag = 1;
+  return false;
+}
+// Sum of the world slots for four consecutive columns of one token row, in rank order.
+__device__ __forceinline__ float4 fused_sum4(const PeerFuse& pf, unsigned parity, long long elem) {
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < pf.world; ++s) {
+    const uint2 v = __ldcg(reinterpret_cast<const uint2*>(fused_recv(pf, pf.rank, parity, s) + elem));
+    acc.x += bf16lo_f32(v.x); acc.y += bf16hi_f32(v.x);
+    acc.z += bf16lo_f32(v.y); acc.w += bf16hi_f32(v.y);
+  }
+  return acc;
+}
+
 struct WqParams {
   const __nv_bfloat16* scales;
   const __nv_bfloat16* zeros;
@@ -73,13 +158,43 @@ struct WqParams {
                        // its main loop
   int rows_per;        // cluster mode: token rows each CTA of the cluster reduces
   int rows_inv;        // ceil(65536 / rows_per): row / rows_per == (row * rows_inv) >> 16
+  int epilogue;        // DXB_EPILOGUE_*: what is applied to the bf16 result before it is stored
+  PeerFuse peer;       // peer.world > 1: the sum over ranks is part of this launch (see below)
   long long* trace;    // only used when built with -DDXB_TRACE
 };
 
 
+// tanh-GELU of a value that has already been rounded to bf16, as the reference applies it
+// between the FFN linears (torch gelu(approximate="tanh") on the bf16 output of the up
+// projection, python/dexter/models/dreamzero/model.py:279-285): evaluated in fp32, rounded once.
+__device__ __forceinline__ float gelu_tanh(float v) {
+  const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+  return 0.5f * v * (1.0f + tanhf(inner));
+}
+
+// Four fp32 sums of one token row -> four bf16 outputs, in the reference's order of
+// roundings: round the matmul to bf16, add the bias in bf16 arithmetic (second rounding),
+// then the optional activation on that bf16 value (third rounding).
+__device__ __forceinline__ uint2 finish_row4(float f0, float f1, float f2, float f3,
+                                             const float (&bias4)[4], bool has_bias, int epilogue) {
+  uint32_t r01 = cvt_bf16x2(f1, f0), r23 = cvt_bf16x2(f3, f2);
+  if (has_bias) {
+    const uint32_t b01 = cvt_bf16x2(bf16hi_f32(r01) + bias4[1], bf16lo_f32(r01) + bias4[0]);
+    const uint32_t b23 = cvt_bf16x2(bf16hi_f32(r23) + bias4[3], bf16lo_f32(r23) + bias4[2]);
+    r01 = b01; r23 = b23;
+  }
+  if (epilogue == DXB_EPILOGUE_GELU_TANH) {
+    r01 = cvt_bf16x2(gelu_tanh(bf16hi_f32(r01)), gelu_tanh(bf16lo_f32(r01)));
+    r23 = cvt_bf16x2(gelu_tanh(bf16hi_f32(r23)), gelu_tanh(bf16lo_f32(r23)));
+  }
+  return make_uint2(r01, r23);
+}
+
 // MULTI: more than one token block (M > 128); a tile is then a (token block, column tile)
 // pair.  The single-block kernel carries none of that bookkeeping.
-template <int BITS, bool HAS_ZERO, bool MULTI>
+// RELAID (int4 only): the packed bytes were rewritten by wq_relayout_w4_kernel so that one
+// 32-bit word holds the k-pairs the TMEM store wants (see there); saves the byte permutes.
+template <int BITS, bool HAS_ZERO, bool MULTI, bool RELAID>
 __global__ void __launch_bounds__(kThreads, 1)
 wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_x,
            const WqParams p) {
@@ -94,7 +209,6 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __shared__ __align__(8) uint64_t bars[kNumBars];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
-  __shared__ int last_flag;
   __shared__ long long t_start;
 
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -104,30 +218,6 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int SW = p.w_stages;
-
-  if (warp == 3) {
-    for (int i = lane; i < kNumBars; i += 32) mbar_init(bar0 + 8 * i, bar_count(i));
-    if (lane == 0) {
-      t_start = clock64();
-      abort_flag = 0;
-      last_flag = 0;
-    }
-    mbar_init_fence();
-  } else if (warp == 0 && lane == 0) {
-    tma_prefetch_desc(&tm_q);
-  } else if (warp == 2 && lane == 0) {
-    tma_prefetch_desc(&tm_x);
-  } else if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_s), 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem0 = tmem_base_s;
-  // The next kernel of the stream may start now: its weight loads and conversion do not
-  // depend on this kernel; it waits (pdl_wait) before it touches activations or outputs.
-  pdl_launch_dependents();
 
   // This CTA's contiguous range of (tile, unit) work.
   // Cluster mode: the `cluster` CTAs of one cluster share one tile, each taking a
@@ -145,6 +235,59 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                           : static_cast<int>(range_begin(blockIdx.x + 1, TU, G));
   const int tile_begin = u_begin / U;
   const int ku_begin = u_begin - tile_begin * U;
+
+  // Packed-weight producers (warps 0 and 3, alternate units): cursor of the next unit to load.
+  // They start BEFORE the CTA-wide set-up barrier: the weights depend on nothing (not on the
+  // previous kernel of the stream either), and the first bytes from HBM are the longest
+  // latency of a short launch.  Each producer initialises the "full" barriers of its own
+  // stages, fences, and fills its half of the ring; the loop after the barrier carries on.
+  const int wp = warp == 0 ? 0 : 1;
+  int w_u = u_begin + wp, w_tile = tile_begin, w_ku = ku_begin + wp, w_s = wp, w_ntile = 0;
+  uint32_t w_ph = 0;
+  auto w_issue = [&]() {
+    if (elect_one()) {
+      const uint32_t fw = bar0 + 8 * (kBarFullW + w_s);
+      mbar_expect_tx(fw, W_STAGE);
+      tma_load_2d(w_ring + w_s * W_STAGE, &tm_q, fw, (MULTI ? w_ntile : w_tile) * kTileN, w_ku * UNIT_ROWS);
+    }
+    __syncwarp();
+    w_u += 2;
+    w_s += 2;
+    if (w_s >= SW) { w_s -= SW; w_ph ^= 1u; }
+    w_ku += 2;
+    while (w_ku >= U) { w_ku -= U; ++w_tile; if (MULTI && ++w_ntile == p.tiles_n) w_ntile = 0; }
+  };
+  if (warp == 0 || warp == 3) {
+    if (lane == 0) tma_prefetch_desc(&tm_q);
+    // full_w barriers of this producer's stages (even stages: warp 0, odd: warp 3); warp 3
+    // also initialises every other barrier, which nobody touches before the barrier below
+    for (int i = wp + 2 * lane; i < kBarEmptyW; i += 64) mbar_init(bar0 + 8 * i, bar_count(i));
+    if (warp == 3) {
+      for (int i = kBarEmptyW + lane; i < kNumBars; i += 32) mbar_init(bar0 + 8 * i, bar_count(i));
+      if (lane == 0) {
+        t_start = clock64();
+        abort_flag = 0;
+      }
+    }
+    mbar_init_fence();
+    __syncwarp();
+    while (w_ku >= U) { w_ku -= U; ++w_tile; }
+    w_ntile = MULTI ? w_tile % p.tiles_n : 0;
+    for (int first = 0; first < (SW >> 1) && w_u < u_end; ++first) w_issue();
+  } else if (warp == 2 && lane == 0) {
+    tma_prefetch_desc(&tm_x);
+  } else if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem0 = tmem_base_s;
+  // The next kernel of the stream may start now: its weight loads and conversion do not
+  // depend on this kernel; it waits (pdl_wait) before it touches activations or outputs.
+  pdl_launch_dependents();
+
   volatile int* abortp = &abort_flag;
 
   // Cluster mode: send this CTA's fp32 partial rows from accumulator `d_tmem` (already
@@ -174,29 +317,14 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // ============================================ TMA producer: packed weights
     // Two producer warps (0 and 3) take alternate units, which doubles the issue rate.
     // The whole warp runs the loop (so addresses and coordinates stay in uniform
-    // registers, which the TMA instruction wants); one elected lane issues.
+    // registers, which the TMA instruction wants); one elected lane issues.  The first
+    // pass over the ring was issued before the set-up barrier (see above).
     {
-      const int pi = warp == 0 ? 0 : 1;
-      int tile = tile_begin, ku = ku_begin + pi, s = pi;
-      while (ku >= U) { ku -= U; ++tile; }
-      int ntile = MULTI ? tile % p.tiles_n : 0;
-      uint32_t ph = 0;
-      int issued = 0;
       bool ok = true;
-      for (int u = u_begin + pi; u < u_end; u += 2) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarEmptyW + s), ph ^ 1u, abortp));
+      while (w_u < u_end) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarEmptyW + w_s), w_ph ^ 1u, abortp));
         if (!ok) break;
-        if (elect_one()) {
-          const uint32_t fw = bar0 + 8 * (kBarFullW + s);
-          mbar_expect_tx(fw, W_STAGE);
-          tma_load_2d(w_ring + s * W_STAGE, &tm_q, fw, (MULTI ? ntile : tile) * kTileN, ku * UNIT_ROWS);
-        }
-        __syncwarp();
-        ++issued;
-        s += 2;
-        if (s >= SW) { s -= SW; ph ^= 1u; }
-        ku += 2;
-        while (ku >= U) { ku -= U; ++tile; if (MULTI && ++ntile == p.tiles_n) ntile = 0; }
+        w_issue();
       }
       if (!ok && lane == 0) {
         // Leaving early: let the copies already issued land before the CTA exits.
@@ -311,6 +439,37 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const int g = lane >> 2;
     const int n_local = 32 * q + 4 * g;
     const bool has_bias = p.bias != nullptr;
+    // Sum over ranks fused into this launch (one token block only): finished rows go to
+    // every rank's receive buffer instead of `out`; fused_finish then completes the tile.
+    const bool fused = p.peer.world > 1;
+    const unsigned parity =
+        fused ? (__ldcg(reinterpret_cast<const unsigned*>(p.peer.region[p.peer.rank])) & 1u) : 0u;
+    auto fused_finish = [&](int ntile, int m_rows) -> bool {
+      __threadfence_system();
+      named_bar_sync(1, kEpilogueThreads);
+      if (etid < p.peer.world) {
+        fused_signal(p.peer, ntile, etid, static_cast<unsigned>(m_rows));
+        fused_wait(p.peer, ntile, etid, static_cast<unsigned>(m_rows), abortp);
+      }
+      named_bar_sync(1, kEpilogueThreads);
+      if (*abortp) return false;
+      const int c4 = (etid & 31) * 4;
+      const int nn = ntile * kTileN + c4;
+      if (nn < p.N) {
+        float b4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (has_bias) {
+          const uint2 bb = __ldg(reinterpret_cast<const uint2*>(p.bias + nn));
+          b4[0] = bf16lo_f32(bb.x); b4[1] = bf16hi_f32(bb.x);
+          b4[2] = bf16lo_f32(bb.y); b4[3] = bf16hi_f32(bb.y);
+        }
+        for (int m = etid >> 5; m < m_rows; m += kEpilogueThreads / 32) {
+          const float4 a = fused_sum4(p.peer, parity, static_cast<long long>(m) * p.N + nn);
+          *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.ldo + nn) =
+              finish_row4(a.x, a.y, a.z, a.w, b4, has_bias, p.epilogue);
+        }
+      }
+      return true;
+    };
     int b = 0;
     uint32_t accph = 0;
     bool ok = true;
@@ -329,7 +488,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       // The bias does not depend on the accumulator: fetch it before waiting, so that its
       // latency is not added to the tail of the tile.
       float bias4[4] = {0.f, 0.f, 0.f, 0.f};
-      if (whole && has_bias && n_ok) {
+      if (ku0 == 0 && has_bias && n_ok) {  // whole tiles and shared tiles this CTA finishes
         const uint2 bb = __ldg(reinterpret_cast<const uint2*>(p.bias + n));
         bias4[0] = bf16lo_f32(bb.x); bias4[1] = bf16hi_f32(bb.x);
         bias4[2] = bf16lo_f32(bb.y); bias4[3] = bf16hi_f32(bb.y);
@@ -348,25 +507,22 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           for (int rep = 0; rep < 4; ++rep) {
             const int m = c0 + 4 * rep + c;
             if (n_ok && m < m_rows) {
-              const float f[4] = {__uint_as_float(ra[2 * rep]), __uint_as_float(ra[2 * rep + 1]),
-                                  __uint_as_float(rb[2 * rep]), __uint_as_float(rb[2 * rep + 1])};
-              uint2 pk;
-              if (has_bias) {
-                // Reference order: round the matmul to bf16, then add the bias in bf16.
-                const uint32_t r01 = cvt_bf16x2(f[1], f[0]), r23 = cvt_bf16x2(f[3], f[2]);
-                pk.x = cvt_bf16x2(bf16hi_f32(r01) + bias4[1], bf16lo_f32(r01) + bias4[0]);
-                pk.y = cvt_bf16x2(bf16hi_f32(r23) + bias4[3], bf16lo_f32(r23) + bias4[2]);
-              } else {
-                pk.x = cvt_bf16x2(f[1], f[0]);
-                pk.y = cvt_bf16x2(f[3], f[2]);
-              }
-              *reinterpret_cast<uint2*>(p.out + static_cast<long long>(row0 + m) * p.ldo + n) = pk;
+              if (fused)
+                fused_push4(p.peer, parity, static_cast<long long>(m) * p.N + n,
+                            __uint_as_float(ra[2 * rep]), __uint_as_float(ra[2 * rep + 1]),
+                            __uint_as_float(rb[2 * rep]), __uint_as_float(rb[2 * rep + 1]));
+              else
+                *reinterpret_cast<uint2*>(p.out + static_cast<long long>(row0 + m) * p.ldo + n) =
+                    finish_row4(__uint_as_float(ra[2 * rep]), __uint_as_float(ra[2 * rep + 1]),
+                                __uint_as_float(rb[2 * rep]), __uint_as_float(rb[2 * rep + 1]),
+                                bias4, has_bias, p.epilogue);
             }
           }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
+        if (fused && !fused_finish(ntile, m_rows)) { ok = false; break; }
       } else if (C > 1) {
         // Cluster mode: CTA r of the cluster finishes token rows [r*rows_per, (r+1)*rows_per)
         // of the tile.  Every CTA sends each owner its fp32 partial rows straight from the
@@ -384,101 +540,96 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           if (lane == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
         }
       } else {
-        // Partial tile: park the fp32 sums, then whoever completes the tile reduces.
+        // A tile shared by several CTAs (equal unit ranges cut it): the CTA that holds the
+        // tile's first units finishes it.  Ranges are contiguous and worked through in
+        // order, so a CTA contributes to a tile it does not finish as its FIRST segment
+        // and finishes a shared tile as its LAST one: by then the contributions have
+        // normally been waiting in global scratch for a while, and the finisher only adds
+        // them to its own accumulator (own sum first, then the slots in CTA order: the
+        // result does not depend on timing).
         const int c_first = owner_of(static_cast<long long>(tile) * U, TU, G);
         const int c_last = owner_of(static_cast<long long>(tile) * U + U - 1, TU, G);
-        const int slot = static_cast<int>(blockIdx.x) - c_first;
         const long long slot_elems = static_cast<long long>(p.NU) * kTileN;
         float* tile_ws = p.partials + static_cast<long long>(tile) * p.max_slots * slot_elems;
-        float* ws = tile_ws + slot * slot_elems;
-        for (int c0 = 0; c0 < p.NU; c0 += 16) {
-          uint32_t ra[8], rb[8];
-          tmem_ld_16x128b_x4(d_tmem + c0, ra);
-          tmem_ld_16x128b_x4(d_tmem + (16u << 16) + c0, rb);
-          tc_wait_ld();
+        if (ku0 > 0) {
+          // contributor: park the fp32 sums, publish, carry on
+          float* ws = tile_ws + (static_cast<int>(blockIdx.x) - c_first - 1) * slot_elems;
+          for (int c0 = 0; c0 < p.NU; c0 += 16) {
+            uint32_t ra[8], rb[8];
+            tmem_ld_16x128b_x4(d_tmem + c0, ra);
+            tmem_ld_16x128b_x4(d_tmem + (16u << 16) + c0, rb);
+            tc_wait_ld();
 #pragma unroll
-          for (int rep = 0; rep < 4; ++rep) {
-            const int m = c0 + 4 * rep + c;
-            if (m < m_rows)
-              __stcg(reinterpret_cast<float4*>(ws + m * kTileN + n_local),
-                     make_float4(__uint_as_float(ra[2 * rep]), __uint_as_float(ra[2 * rep + 1]),
-                                 __uint_as_float(rb[2 * rep]), __uint_as_float(rb[2 * rep + 1])));
+            for (int rep = 0; rep < 4; ++rep) {
+              const int m = c0 + 4 * rep + c;
+              if (m < m_rows)
+                __stcg(reinterpret_cast<float4*>(ws + m * kTileN + n_local),
+                       make_float4(__uint_as_float(ra[2 * rep]), __uint_as_float(ra[2 * rep + 1]),
+                                   __uint_as_float(rb[2 * rep]), __uint_as_float(rb[2 * rep + 1])));
+            }
           }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
-        __threadfence();
-        named_bar_sync(1, kEpilogueThreads);
-        if (etid == 0) {
-          const int old = atomicAdd(&p.counters[tile], nun);
-          const int last = (old + nun == U) ? 1 : 0;
-          if (last) p.counters[tile] = 0;  // ready for the next launch / graph replay
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
           __threadfence();
-          last_flag = last;
-        }
-        named_bar_sync(1, kEpilogueThreads);
-        if (last_flag) {
-          // 128 threads = 32 groups of 4 columns x 4 row phases; slots are summed in
-          // slot order, so the result does not depend on which CTA arrives last.
-          const int nslots = c_last - c_first + 1;
-          const int col4 = (etid & 31) * 4;
-          const int nn = ntile * kTileN + col4;
-          if (nn < p.N) {
-            float bias4[4] = {0.f, 0.f, 0.f, 0.f};
-            if (has_bias) {
+          named_bar_sync(1, kEpilogueThreads);
+          if (etid == 0) atomicAdd(&p.counters[tile], 1);
+        } else {
+          // finisher: wait (bounded) until every contributor has published
+          const int ncontrib = c_last - c_first;
+          if (etid == 0) {
+            if (wait_flag_ge(&p.counters[tile], ncontrib, abortp))
+              p.counters[tile] = 0;  // ready for the next launch / graph replay
+          }
+          named_bar_sync(1, kEpilogueThreads);
+          if (*abortp) { ok = false; break; }
+          for (int c0 = 0; c0 < p.NU; c0 += 16) {
+            float4 v[4];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) bias4[j] = __bfloat162float(p.bias[nn + j]);
-            }
-            for (int m0 = etid >> 5; m0 < m_rows; m0 += 16) {
-              float4 acc[4];
+            for (int rep = 0; rep < 4; ++rep) v[rep] = make_float4(0.f, 0.f, 0.f, 0.f);
+            // contributions in CTA order; the loads of one slot are in flight together
+            for (int sl = 0; sl < ncontrib; ++sl) {
+              float4 t4[4];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-              // Two slots (eight 16-byte loads) in flight per thread: the reduce is bound by
-              // L2 latency, not bandwidth.  The additions stay in slot order.
-              for (int sl = 0; sl < nslots; sl += 2) {
-                float4 v[8];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    const int m = m0 + 4 * j;
-                    v[4 * h + j] = (m < m_rows && sl + h < nslots)
-                                       ? __ldcg(reinterpret_cast<const float4*>(
-                                             tile_ws + (sl + h) * slot_elems + m * kTileN + col4))
-                                       : make_float4(0.f, 0.f, 0.f, 0.f);
-                  }
-                }
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    acc[j].x += v[4 * h + j].x; acc[j].y += v[4 * h + j].y;
-                    acc[j].z += v[4 * h + j].z; acc[j].w += v[4 * h + j].w;
-                  }
-                }
+              for (int rep = 0; rep < 4; ++rep) {
+                const int m = c0 + 4 * rep + c;
+                t4[rep] = m < m_rows ? __ldcg(reinterpret_cast<const float4*>(
+                                           tile_ws + sl * slot_elems + m * kTileN + n_local))
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
               }
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int m = m0 + 4 * j;
-                if (m < m_rows) {
-                  uint2 pk;
-                  if (has_bias) {
-                    const uint32_t r01 = cvt_bf16x2(acc[j].y, acc[j].x);
-                    const uint32_t r23 = cvt_bf16x2(acc[j].w, acc[j].z);
-                    pk.x = cvt_bf16x2(bf16hi_f32(r01) + bias4[1], bf16lo_f32(r01) + bias4[0]);
-                    pk.y = cvt_bf16x2(bf16hi_f32(r23) + bias4[3], bf16lo_f32(r23) + bias4[2]);
-                  } else {
-                    pk.x = cvt_bf16x2(acc[j].y, acc[j].x);
-                    pk.y = cvt_bf16x2(acc[j].w, acc[j].z);
-                  }
-                  *reinterpret_cast<uint2*>(p.out + static_cast<long long>(row0 + m) * p.ldo + nn) = pk;
+              for (int rep = 0; rep < 4; ++rep) {
+                if (sl == 0) {
+                  v[rep] = t4[rep];
+                } else {
+                  v[rep].x += t4[rep].x; v[rep].y += t4[rep].y;
+                  v[rep].z += t4[rep].z; v[rep].w += t4[rep].w;
                 }
+              }
+            }
+            uint32_t ra[8], rb[8];
+            tmem_ld_16x128b_x4(d_tmem + c0, ra);
+            tmem_ld_16x128b_x4(d_tmem + (16u << 16) + c0, rb);
+            tc_wait_ld();
+#pragma unroll
+            for (int rep = 0; rep < 4; ++rep) {
+              const int m = c0 + 4 * rep + c;
+              if (n_ok && m < m_rows) {
+                const float f0 = __uint_as_float(ra[2 * rep]) + v[rep].x, f1 = __uint_as_float(ra[2 * rep + 1]) + v[rep].y;
+                const float f2 = __uint_as_float(rb[2 * rep]) + v[rep].z, f3 = __uint_as_float(rb[2 * rep + 1]) + v[rep].w;
+                if (fused)
+                  fused_push4(p.peer, parity, static_cast<long long>(m) * p.N + n, f0, f1, f2, f3);
+                else
+                  *reinterpret_cast<uint2*>(p.out + static_cast<long long>(row0 + m) * p.ldo + n) =
+                      finish_row4(f0, f1, f2, f3, bias4, has_bias, p.epilogue);
               }
             }
           }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
+          if (fused && !fused_finish(ntile, m_rows)) { ok = false; break; }
         }
-        named_bar_sync(1, kEpilogueThreads);  // last_flag is reused by the next segment
       }
       u += nun;
       ku0 = 0;
@@ -583,12 +734,24 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
             uint32_t ra[8], rb[8];
 #pragma unroll
             for (int sl = 0; sl < 4; ++sl) {
-              const uint32_t P = prmt(w0[4 * rh + sl], w1[4 * rh + sl], 0x5410u) >> (4 * pl);
-              const uint32_t Q = prmt(w0[4 * rh + sl], w1[4 * rh + sl], 0x7632u) >> (4 * pl);
-              ra[2 * sl + 0] = deq4(P, z2[0], s2[0]);
-              ra[2 * sl + 1] = deq4(P >> 8, z2[1], s2[1]);
-              rb[2 * sl + 0] = deq4(Q, z2[2], s2[2]);
-              rb[2 * sl + 1] = deq4(Q >> 8, z2[3], s2[3]);
+              if (RELAID) {
+                // The word of the even row holds the low-nibble plane, the word of the odd
+                // row the high-nibble plane: nibble b is byte column b of the even row,
+                // nibble 4 + b the same column of the odd row, so masking with 0x000F000F
+                // after a shift by 4b yields the k-pair of column b directly.
+                const uint32_t W = pl == 0 ? w0[4 * rh + sl] : w1[4 * rh + sl];
+                ra[2 * sl + 0] = deq4(W, z2[0], s2[0]);
+                ra[2 * sl + 1] = deq4(W >> 4, z2[1], s2[1]);
+                rb[2 * sl + 0] = deq4(W >> 8, z2[2], s2[2]);
+                rb[2 * sl + 1] = deq4(W >> 12, z2[3], s2[3]);
+              } else {
+                const uint32_t P = prmt(w0[4 * rh + sl], w1[4 * rh + sl], 0x5410u) >> (4 * pl);
+                const uint32_t Q = prmt(w0[4 * rh + sl], w1[4 * rh + sl], 0x7632u) >> (4 * pl);
+                ra[2 * sl + 0] = deq4(P, z2[0], s2[0]);
+                ra[2 * sl + 1] = deq4(P >> 8, z2[1], s2[1]);
+                rb[2 * sl + 0] = deq4(Q, z2[2], s2[2]);
+                rb[2 * sl + 1] = deq4(Q >> 8, z2[3], s2[3]);
+              }
             }
             tmem_st_16x128b_x4(tmem_addr(a_tmem + pl * 32 + 16 * rh, lane_base, 0), ra);
             tmem_st_16x128b_x4(tmem_addr(a_tmem + pl * 32 + 16 * rh, lane_base + 16, 0), rb);
@@ -684,6 +847,9 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // remote is touched any more, so CTAs leave independently.
     cluster_sync_all();
     pdl_wait();
+    const bool fused = p.peer.world > 1;
+    const unsigned parity =
+        fused ? (__ldcg(reinterpret_cast<const unsigned*>(p.peer.region[p.peer.rank])) & 1u) : 0u;
     if (n < p.N) {
       for (int i = threadIdx.x; i < (m_hi - m_lo) * 32; i += kThreads) {
         const int j = i >> 5;
@@ -697,16 +863,56 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (int r = 0; r < 8; ++r) {  // rank order: the sum does not depend on timing
           acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w;
         }
-        uint2 pk;
-        if (has_bias) {
-          const uint32_t r01 = cvt_bf16x2(acc.y, acc.x), r23 = cvt_bf16x2(acc.w, acc.z);
-          pk.x = cvt_bf16x2(bf16hi_f32(r01) + bias4[1], bf16lo_f32(r01) + bias4[0]);
-          pk.y = cvt_bf16x2(bf16hi_f32(r23) + bias4[3], bf16lo_f32(r23) + bias4[2]);
-        } else {
-          pk.x = cvt_bf16x2(acc.y, acc.x);
-          pk.y = cvt_bf16x2(acc.w, acc.z);
+        if (fused)
+          fused_push4(p.peer, parity, static_cast<long long>(m_lo + j) * p.N + n, acc.x, acc.y, acc.z, acc.w);
+        else
+          *reinterpret_cast<uint2*>(p.out + static_cast<long long>(row0 + m_lo + j) * p.ldo + n) =
+              finish_row4(acc.x, acc.y, acc.z, acc.w, bias4, has_bias, p.epilogue);
+      }
+    }
+    if (fused) {
+      // This CTA's rows of the tile are on their way to every rank: publish them, wait for
+      // the whole tile from every rank, then finish this CTA's rows from the local slots.
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x < p.peer.world && m_hi > m_lo) {  // a CTA without rows has nothing to do
+        fused_signal(p.peer, ntile, threadIdx.x, static_cast<unsigned>(m_hi - m_lo));
+        fused_wait(p.peer, ntile, threadIdx.x, static_cast<unsigned>(m_rows), abortp);
+      }
+      __syncthreads();
+      if (!abort_flag && n < p.N) {
+        for (int i = threadIdx.x; i < (m_hi - m_lo) * 32; i += kThreads) {
+          const int m = m_lo + (i >> 5);
+          const float4 a = fused_sum4(p.peer, parity, static_cast<long long>(m) * p.N + n);
+          *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.ldo + n) =
+              finish_row4(a.x, a.y, a.z, a.w, bias4, has_bias, p.epilogue);
         }
-        *reinterpret_cast<uint2*>(p.out + static_cast<long long>(row0 + m_lo + j) * p.ldo + n) = pk;
+      }
+    }
+  }
+  if (p.peer.world > 1) {
+    // The last CTA to leave moves the per-tile row baselines and the epoch on for the next
+    // call (every other CTA has finished reading them by then).
+    __shared__ int is_last;
+    __syncthreads();
+    unsigned char* mine = p.peer.region[p.peer.rank];
+    unsigned* control = reinterpret_cast<unsigned*>(mine);
+    if (threadIdx.x == 0) {
+      __threadfence();
+      is_last = atomicAdd(control + 1, 1u) == gridDim.x - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (is_last) {
+      __threadfence();
+      for (int i = threadIdx.x; i < p.tiles_n * p.peer.world; i += kThreads) {
+        unsigned* bp = fused_base(mine, i / p.peer.world, i % p.peer.world);
+        *bp = __ldcg(bp) + static_cast<unsigned>(p.M);
+      }
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        control[1] = 0;
+        control[0] = __ldcg(control) + 1;
       }
     }
   }
@@ -718,13 +924,56 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   }
 }
 
+// ------------------------------------------------ load-time weight re-layout
+// int4 only.  The reference packs byte [i, n] = row i (low nibble) | row i + K/2 (high
+// nibble) (python/dexter/quant.py:62-72).  For every aligned block of 2 packed rows x 4
+// byte columns (the two 32-bit words one dequant thread reads per slab of 8 rows) the 16
+// nibbles are regrouped: the word at the even row keeps the low-nibble plane, the word at
+// the odd row the high-nibble plane; inside a word, nibble b (bits 4b..4b+3) is byte column b
+// of the even row and nibble 4 + b the same column of the odd row.  `(word >> 4b) &
+// 0x000F000F` is then the bf16x2 mantissa pair (k, k+1) of column b: no byte permute.
+// Same shape, same strides, same tiles; the transform is its own inverse pair (forward /
+// inverse below) and is applied once per weight, never per call.
+__device__ __forceinline__ uint32_t squeeze_nibbles(uint32_t v) {  // nibbles at bits 0,8,16,24 -> 0,4,8,12
+  return (v & 0xFu) | ((v >> 4) & 0xF0u) | ((v >> 8) & 0xF00u) | ((v >> 12) & 0xF000u);
+}
+__device__ __forceinline__ uint32_t spread_nibbles(uint32_t h) {   // nibbles at bits 0,4,8,12 -> 0,8,16,24
+  return (h & 0xFu) | ((h & 0xF0u) << 4) | ((h & 0xF00u) << 8) | ((h & 0xF000u) << 12);
+}
+__global__ void wq_relayout_w4_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
+                                      long long row_pairs, int n4, int inverse) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= row_pairs * n4) return;
+  const long long rp = idx / n4;
+  const int j = static_cast<int>(idx - rp * n4);
+  const long long i0 = (2 * rp) * n4 + j, i1 = (2 * rp + 1) * n4 + j;
+  const uint32_t w0 = in[i0], w1 = in[i1];
+  if (!inverse) {
+    out[i0] = squeeze_nibbles(w0 & 0x0F0F0F0Fu) | (squeeze_nibbles(w1 & 0x0F0F0F0Fu) << 16);
+    out[i1] = squeeze_nibbles((w0 >> 4) & 0x0F0F0F0Fu) | (squeeze_nibbles((w1 >> 4) & 0x0F0F0F0Fu) << 16);
+  } else {
+    out[i0] = spread_nibbles(w0 & 0xFFFFu) | (spread_nibbles(w1 & 0xFFFFu) << 4);
+    out[i1] = spread_nibbles(w0 >> 16) | (spread_nibbles(w1 >> 16) << 4);
+  }
+}
+
+// Value 0..15 of logical row k, column n of an int4 weight in either layout.
+__device__ __forceinline__ uint32_t fetch_q4(const uint8_t* __restrict__ qw, int N, int half, int k, int n,
+                                             int relaid) {
+  const int plane = k < half ? 0 : 1;
+  const int r = k - plane * half;  // packed row
+  if (!relaid) return (qw[static_cast<long long>(r) * N + n] >> (4 * plane)) & 0xFu;
+  const uint32_t word = reinterpret_cast<const uint32_t*>(qw)[(static_cast<long long>(r & ~1) + plane) * (N >> 2) + (n >> 2)];
+  return (word >> (16 * (r & 1) + 4 * (n & 3))) & 0xFu;
+}
+
 // --------------------------------------------- dense dequantised weight dump
 // W[k,n] bf16 with the same bit-pattern arithmetic as the tensor-core kernel;
 // used to check the dequantisation bit for bit against the reference.
 template <int BITS>
 __global__ void wq_dequant_kernel(const uint8_t* __restrict__ qw, const __nv_bfloat16* __restrict__ scales,
                                   const __nv_bfloat16* __restrict__ zeros, __nv_bfloat16* __restrict__ out,
-                                  int N, int K, int group) {
+                                  int N, int K, int group, int relaid) {
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long total = static_cast<long long>(K) * N;
   if (idx >= total) return;
@@ -733,9 +982,7 @@ __global__ void wq_dequant_kernel(const uint8_t* __restrict__ qw, const __nv_bfl
   const int gi = k / group;
   const uint32_t sbits = __bfloat16_as_ushort(scales[static_cast<long long>(gi) * N + n]);
   if (BITS == 4) {
-    const int half = K / 2;
-    const uint32_t byte = k < half ? qw[static_cast<long long>(k) * N + n]
-                                   : (qw[static_cast<long long>(k - half) * N + n] >> 4);
+    const uint32_t byte = fetch_q4(qw, N, K / 2, k, n, relaid);
     const uint32_t z = zeros ? __bfloat16_as_ushort(zeros[static_cast<long long>(gi) * N + n]) : 0x4308u;
     const uint32_t r = deq4(byte, z | (z << 16), sbits | (sbits << 16));
     out[idx] = __ushort_as_bfloat16(static_cast<unsigned short>(r & 0xFFFFu));
@@ -756,7 +1003,7 @@ template <int BITS>
 __global__ void wq_gemm_simt(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t* __restrict__ qw,
                              const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ zeros,
                              const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, long long ldo,
-                             int M, int N, int K, int group) {
+                             int M, int N, int K, int group, int relaid, int epilogue) {
   constexpr int MT = 8;
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
   const int m0 = blockIdx.y * MT;
@@ -770,8 +1017,7 @@ __global__ void wq_gemm_simt(const __nv_bfloat16* __restrict__ x, long long ldx,
     const uint32_t sbits = __bfloat16_as_ushort(scales[static_cast<long long>(gi) * N + n]);
     float w;
     if (BITS == 4) {
-      const uint32_t byte = k < half ? qw[static_cast<long long>(k) * N + n]
-                                     : (qw[static_cast<long long>(k - half) * N + n] >> 4);
+      const uint32_t byte = fetch_q4(qw, N, half, k, n, relaid);
       const uint32_t z = zeros ? __bfloat16_as_ushort(zeros[static_cast<long long>(gi) * N + n]) : 0x4308u;
       w = __uint_as_float(deq4(byte, z | (z << 16), sbits | (sbits << 16)) << 16);
     } else {
@@ -788,6 +1034,7 @@ __global__ void wq_gemm_simt(const __nv_bfloat16* __restrict__ x, long long ldx,
     if (m0 + i < M) {
       __nv_bfloat16 o = __float2bfloat16_rn(acc[i]);
       if (bias) o = __float2bfloat16_rn(__bfloat162float(o) + __bfloat162float(bias[n]));
+      if (epilogue == DXB_EPILOGUE_GELU_TANH) o = __float2bfloat16_rn(gelu_tanh(__bfloat162float(o)));
       out[static_cast<long long>(m0 + i) * ldo + n] = o;
     }
 }
@@ -795,6 +1042,10 @@ __global__ void wq_gemm_simt(const __nv_bfloat16* __restrict__ x, long long ldx,
 // ------------------------------------------------------------------ host side
 static long long* g_trace = nullptr;
 
+// Upper bound of the polled waits on flags that another GPU writes, in polls of about a
+// quarter of a microsecond (default: about a second).
+static std::atomic<unsigned> g_wait_tries{4000000u};
+unsigned wait_tries() { return g_wait_tries.load(std::memory_order_relaxed); }
 
 // Programmatic dependent launch is on unless DEXTER_B200_PDL=0.
 static bool pdl_enabled() {
@@ -805,6 +1056,14 @@ static bool pdl_enabled() {
   return on;
 }
 
+// What a call asks for beyond the plain GEMM (dxb_gemm_opts, checked and copied).
+struct Opts {
+  int relaid = 0;
+  int epilogue = DXB_EPILOGUE_NONE;
+  int max_ctas = 0;
+  PeerFuse peer = {};
+};
+
 struct Plan {
   int NU, planes, rows, unit_rows, w_stage_bytes, units_per_tile, tiles, tiles_n, total_units, stages,
       w_stages, x_stage_bytes, ctas,
@@ -812,8 +1071,18 @@ struct Plan {
   size_t smem_bytes;
 };
 
+// Cost, in units, of finishing a tile that equal unit ranges cut between CTAs: the finisher
+// reads the other CTAs' fp32 partial tiles from L2 and adds them to its accumulator.
+static int fixup_units(int NU) {
+  static const int forced = [] {
+    const char* e = getenv("DEXTER_B200_FIXUP_UNITS");
+    return e ? atoi(e) : -1;
+  }();
+  if (forced >= 0) return forced;
+  return NU > 96 ? 6 : 4;
+}
 
-static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
+static Plan make_plan_uncached(int M, int N, int K, int bits, int sms, int max_ctas, bool allow_split) {
   Plan pl{};
   // More than 128 tokens: token blocks of 128, each (block, column tile) pair is a tile of
   // its own, so one launch covers all of them and every SM stays busy.
@@ -859,20 +1128,18 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   pl.smem_bytes = static_cast<size_t>(rings) + (pl.recv_alias ? 0 : pl.recv_bytes) + 1024;
   // Grid: `budget` CTAs at most (all SMs unless the caller caps it, e.g. to run several
   // GEMMs side by side).
-  const int budget = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
+  const int budget = budget_ctas;
   // Two ways to hand out the work.  Whole tiles: every CTA takes `rounds` complete tiles
-  // (CTAs may idle, nothing is split).  Equal unit ranges over all CTAs (stream-K): nobody
-  // idles, but the tiles cut by a range boundary go through global scratch, which costs
-  // as much as a few dozen units.  Take whichever ends sooner.  (Few tiles in one token block
-  // are split over clusters instead; the launcher decides that, see launch_tc.)
+  // (CTAs may idle, nothing is split).  Equal unit ranges over all CTAs: nobody idles, but
+  // the tiles cut by a range boundary are finished through global scratch (see the
+  // epilogue).  Take whichever ends sooner.  (Few tiles in one token block are split over
+  // clusters instead; the launcher decides that, see launch_tc.)
   const int rounds = (pl.tiles + budget - 1) / budget;
   const int whole_ctas = (pl.tiles + rounds - 1) / rounds;
   const long long whole_units = static_cast<long long>(rounds) * pl.units_per_tile;
-  // measured cost of the global fix-up in units: ~16 at <= 96 tokens, ~28 with 128-token
-  // accumulators (larger partial tiles)
-  const int fixup_units = pl.NU > 96 ? 28 : 16;
-  const long long split_units = (pl.total_units + budget - 1) / budget + fixup_units;
-  int ctas = (pl.tiles % whole_ctas == 0 && whole_units <= split_units) ? whole_ctas : budget;
+  const long long split_units = (pl.total_units + budget - 1) / budget + fixup_units(pl.NU);
+  const bool whole = !allow_split || (pl.tiles % whole_ctas == 0 && whole_units <= split_units);
+  int ctas = whole ? whole_ctas : budget;
   if (ctas > pl.total_units) ctas = pl.total_units;
   pl.ctas = ctas;
   pl.nacc = 2;
@@ -885,6 +1152,30 @@ static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas) {
   }
   pl.max_slots = max_slots;
   return pl;
+}
+
+// Plans only depend on the shape, so they are computed once per shape and thread.
+static Plan make_plan(int M, int N, int K, int bits, int sms, int max_ctas, bool allow_split = true) {
+  struct Key {
+    int M, N, K, bits, sms, max_ctas, split;
+    bool operator==(const Key& o) const {
+      return M == o.M && N == o.N && K == o.K && bits == o.bits && sms == o.sms && max_ctas == o.max_ctas &&
+             split == o.split;
+    }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      size_t h = 1469598103934665603ull;
+      for (int v : {k.M, k.N, k.K, k.bits, k.sms, k.max_ctas, k.split}) h = (h ^ static_cast<size_t>(v)) * 1099511628211ull;
+      return h;
+    }
+  };
+  static thread_local std::unordered_map<Key, Plan, Hash> cache;
+  const Key key{M, N, K, bits, sms, max_ctas, allow_split ? 1 : 0};
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  if (cache.size() > 4096) cache.clear();
+  return cache.emplace(key, make_plan_uncached(M, N, K, bits, sms, max_ctas, allow_split)).first->second;
 }
 
 // The counter block has one fixed size so that calls with different tile counts
@@ -904,43 +1195,141 @@ static size_t plan_workspace_bytes(int M, int N, int K, int bits, int max_ctas) 
          static_cast<size_t>(pl.tiles) * pl.max_slots * pl.NU * kTileN * sizeof(float);
 }
 
+// TMA tensor maps are encoded once per (pointer, geometry) and thread, not per call.
+struct MapKey {
+  const void* ptr;
+  long long a, b, c;
+  int kind;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && a == o.a && b == o.b && c == o.c && kind == o.kind; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr) * 1099511628211ull;
+    for (long long v : {k.a, k.b, k.c, static_cast<long long>(k.kind)}) h = (h ^ static_cast<size_t>(v)) * 1099511628211ull;
+    return h;
+  }
+};
+template <class Encode>
+static const CUtensorMap* cached_map(const MapKey& key, Encode&& encode) {
+  static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  auto it = cache.find(key);
+  if (it != cache.end()) return &it->second;
+  if (cache.size() > 16384) cache.clear();
+  CUtensorMap m;
+  if (!encode(&m)) return nullptr;
+  return &cache.emplace(key, m).first->second;
+}
+
 template <int BITS, bool HAS_ZERO>
 static int launch_tc(const void* x, long long ldx, const void* qw, const void* scales,
                      const void* zeros, const void* bias, void* out, long long ldo, int M, int N,
-                     int K, int group, void* workspace, size_t workspace_bytes, int max_ctas,
+                     int K, int group, void* workspace, size_t workspace_bytes, const Opts& opts,
                      cudaStream_t stream) {
   DeviceInfo& di = device_info();
-  const Plan pl = make_plan(M, N, K, BITS, di.sms, max_ctas);
-  if (pl.w_stages < kAStages) return DXB_ERR_UNSUPPORTED;
+  const int max_ctas = opts.max_ctas;
+  Plan plan = make_plan(M, N, K, BITS, di.sms, max_ctas);
+  const Plan* plp = &plan;
+  if (plp->w_stages < kAStages) return DXB_ERR_UNSUPPORTED;
   // Status word and counters are always needed; the partial sums only if the launch ends up
   // splitting tiles through global scratch (checked below, once the cluster size is known).
-  if (workspace == nullptr || workspace_bytes < kStatusBytes + counters_bytes(pl.tiles))
+  if (workspace == nullptr || workspace_bytes < kStatusBytes + counters_bytes(plp->tiles))
     return DXB_ERR_WORKSPACE;
 
-  CUtensorMap tq, tx;
-  bool ok;
-  {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static thread_local int attr_dev = -1;
+  if (attr_dev != dev) {
+    bool ok = true;
+    auto set = [&](auto kern) {
+      ok = ok && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024) == cudaSuccess;
+    };
+    set(wq_gemm_tc<BITS, HAS_ZERO, true, false>);
+    set(wq_gemm_tc<BITS, HAS_ZERO, false, false>);
+    if (BITS == 4) {
+      set(wq_gemm_tc<BITS, HAS_ZERO, true, BITS == 4>);
+      set(wq_gemm_tc<BITS, HAS_ZERO, false, BITS == 4>);
+    }
+    if (!ok) return DXB_ERR_CUDA;
+    attr_dev = dev;
+  }
+  const bool multi = plp->tiles > plp->tiles_n;
+  const bool relaid = BITS == 4 && opts.relaid;
+  auto kernel = multi ? (relaid ? wq_gemm_tc<BITS, HAS_ZERO, true, BITS == 4> : wq_gemm_tc<BITS, HAS_ZERO, true, false>)
+                      : (relaid ? wq_gemm_tc<BITS, HAS_ZERO, false, BITS == 4> : wq_gemm_tc<BITS, HAS_ZERO, false, false>);
+
+  // Few tiles: split each tile's K range over a thread-block cluster (<= 8 CTAs) that
+  // reduces through distributed shared memory.  The cluster size is the largest one for
+  // which all clusters are resident at once; the answer is cached per configuration.
+  int cluster = 1;
+  const int budget = (max_ctas > 0 && max_ctas < di.sms) ? max_ctas : di.sms;
+  if (plp->recv_bytes > 0 && plp->tiles * 2 <= budget && plp->units_per_tile >= 2) {
+    static thread_local std::unordered_map<long long, int> cache;
+    const long long key = (static_cast<long long>(dev) << 48) ^ (static_cast<long long>(plp->tiles) << 28) ^
+                          (static_cast<long long>(plp->units_per_tile) << 8) ^ static_cast<long long>(plp->NU >> 4) ^
+                          (static_cast<long long>(budget) << 38) ^ (static_cast<long long>(multi) << 58) ^
+                          (static_cast<long long>(relaid) << 59);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      cluster = it->second;
+    } else {
+      int cmax = budget / plp->tiles;
+      if (cmax > 8) cmax = 8;
+      if (cmax > plp->units_per_tile) cmax = plp->units_per_tile;
+      for (int c = cmax; c >= 2; --c) {
+        cudaLaunchConfig_t qcfg = {};
+        qcfg.gridDim = dim3(plp->tiles * c);
+        qcfg.blockDim = dim3(kThreads);
+        qcfg.dynamicSmemBytes = plp->smem_bytes;
+        cudaLaunchAttribute qattr[1];
+        qattr[0].id = cudaLaunchAttributeClusterDimension;
+        qattr[0].val.clusterDim.x = c;
+        qattr[0].val.clusterDim.y = 1;
+        qattr[0].val.clusterDim.z = 1;
+        qcfg.attrs = qattr;
+        qcfg.numAttrs = 1;
+        int resident = 0;
+        if (cudaOccupancyMaxActiveClusters(&resident, kernel, &qcfg) == cudaSuccess &&
+            resident >= plp->tiles) {
+          cluster = c;
+          break;
+        }
+        cudaGetLastError();
+      }
+      cache[key] = cluster;
+    }
+  }
+  if (cluster == 1) {
+    const size_t need = kStatusBytes + counters_bytes(plp->tiles) +
+                        static_cast<size_t>(plp->tiles) * plp->max_slots * plp->NU * kTileN * sizeof(float);
+    if (workspace_bytes < need) {
+      // The workspace was sized for another grid cap: whole tiles need no partial sums.
+      if (plp->max_slots > 1) plan = make_plan(M, N, K, BITS, di.sms, max_ctas, false);
+      if (plp->max_slots > 1) return DXB_ERR_WORKSPACE;
+    }
+  }
+  const Plan& pl = *plp;
+
+  const CUtensorMap* tq = cached_map(MapKey{qw, N, pl.rows, 0, BITS}, [&](CUtensorMap* m) {
     const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(pl.rows)};
     const uint64_t strides[1] = {static_cast<uint64_t>(N)};
     const uint32_t box[2] = {kTileN, static_cast<uint32_t>(pl.unit_rows)};
-    ok = make_map(&tq, qw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, dims, strides, box,
-                  CU_TENSOR_MAP_SWIZZLE_128B);
-  }
-  if (BITS == 4) {
-    // X seen as [plane][token][k within the plane]: one box brings both k-slices of a unit.
-    const uint64_t dims[3] = {static_cast<uint64_t>(K / 2), static_cast<uint64_t>(M), 2};
-    const uint64_t strides[2] = {static_cast<uint64_t>(ldx) * 2, static_cast<uint64_t>(K / 2) * 2};
-    const uint32_t box[3] = {64, static_cast<uint32_t>(pl.NU), 2};
-    ok = ok && make_map(&tx, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box,
-                        CU_TENSOR_MAP_SWIZZLE_128B);
-  } else {
+    return make_map(m, qw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  });
+  const CUtensorMap* tx = cached_map(MapKey{x, ldx, (static_cast<long long>(M) << 32) | K, pl.NU, 16 + BITS},
+                                     [&](CUtensorMap* m) {
+    if (BITS == 4) {
+      // X seen as [plane][token][k within the plane]: one box brings both k-slices of a unit.
+      const uint64_t dims[3] = {static_cast<uint64_t>(K / 2), static_cast<uint64_t>(M), 2};
+      const uint64_t strides[2] = {static_cast<uint64_t>(ldx) * 2, static_cast<uint64_t>(K / 2) * 2};
+      const uint32_t box[3] = {64, static_cast<uint32_t>(pl.NU), 2};
+      return make_map(m, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    }
     const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(ldx) * 2};
     const uint32_t box[2] = {64, static_cast<uint32_t>(pl.NU)};
-    ok = ok && make_map(&tx, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dims, strides, box,
-                        CU_TENSOR_MAP_SWIZZLE_128B);
-  }
-  if (!ok) return DXB_ERR_TENSORMAP;
+    return make_map(m, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  });
+  if (!tq || !tx) return DXB_ERR_TENSORMAP;
 
   WqParams p{};
   p.scales = static_cast<const __nv_bfloat16*>(scales);
@@ -971,65 +1360,8 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
     p.group_shift = sh;
   }
   p.trace = g_trace;
-
-  auto kernel = pl.tiles > pl.tiles_n ? wq_gemm_tc<BITS, HAS_ZERO, true> : wq_gemm_tc<BITS, HAS_ZERO, false>;
-  static thread_local int attr_dev = -1;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (attr_dev != dev) {
-    if (cudaFuncSetAttribute(wq_gemm_tc<BITS, HAS_ZERO, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemBudget + 1024) != cudaSuccess ||
-        cudaFuncSetAttribute(wq_gemm_tc<BITS, HAS_ZERO, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemBudget + 1024) != cudaSuccess)
-      return DXB_ERR_CUDA;
-    attr_dev = dev;
-  }
-
-  // Few tiles: split each tile's K range over a thread-block cluster (<= 8 CTAs) that
-  // reduces through distributed shared memory.  The cluster size is the largest one for
-  // which all clusters are resident at once; the answer is cached per configuration.
-  int cluster = 1;
-  const int budget = (max_ctas > 0 && max_ctas < di.sms) ? max_ctas : di.sms;
-  if (pl.recv_bytes > 0 && pl.tiles * 2 <= budget && pl.units_per_tile >= 2) {
-    static thread_local std::unordered_map<long long, int> cache;
-    const long long key = (static_cast<long long>(dev) << 48) ^ (static_cast<long long>(pl.tiles) << 28) ^
-                          (static_cast<long long>(pl.units_per_tile) << 8) ^ static_cast<long long>(pl.NU >> 4) ^
-                          (static_cast<long long>(budget) << 38);
-    auto it = cache.find(key);
-    if (it != cache.end()) {
-      cluster = it->second;
-    } else {
-      int cmax = budget / pl.tiles;
-      if (cmax > 8) cmax = 8;
-      if (cmax > pl.units_per_tile) cmax = pl.units_per_tile;
-      for (int c = cmax; c >= 2; --c) {
-        cudaLaunchConfig_t qcfg = {};
-        qcfg.gridDim = dim3(pl.tiles * c);
-        qcfg.blockDim = dim3(kThreads);
-        qcfg.dynamicSmemBytes = pl.smem_bytes;
-        cudaLaunchAttribute qattr[1];
-        qattr[0].id = cudaLaunchAttributeClusterDimension;
-        qattr[0].val.clusterDim.x = c;
-        qattr[0].val.clusterDim.y = 1;
-        qattr[0].val.clusterDim.z = 1;
-        qcfg.attrs = qattr;
-        qcfg.numAttrs = 1;
-        int resident = 0;
-        if (cudaOccupancyMaxActiveClusters(&resident, kernel, &qcfg) == cudaSuccess &&
-            resident >= pl.tiles) {
-          cluster = c;
-          break;
-        }
-        cudaGetLastError();
-      }
-      cache[key] = cluster;
-    }
-  }
-  if (cluster == 1) {
-    const size_t need = kStatusBytes + counters_bytes(pl.tiles) +
-                        static_cast<size_t>(pl.tiles) * pl.max_slots * pl.NU * kTileN * sizeof(float);
-    if (workspace_bytes < need) return DXB_ERR_WORKSPACE;
-  }
+  p.epilogue = opts.epilogue;
+  p.peer = opts.peer;
   p.cluster = cluster;
   p.recv_off = pl.recv_off;
   p.recv_alias = cluster > 1 ? pl.recv_alias : 0;
@@ -1059,7 +1391,7 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   }
   cfg.attrs = attr;
   cfg.numAttrs = nattr;
-  if (cudaLaunchKernelEx(&cfg, kernel, tq, tx, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kernel, *tq, *tx, p) != cudaSuccess) {
     cudaGetLastError();
     return DXB_ERR_CUDA;
   }
@@ -1069,12 +1401,13 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
 template <int BITS>
 static int launch_simt(const void* x, long long ldx, const void* qw, const void* scales,
                        const void* zeros, const void* bias, void* out, long long ldo, int M, int N,
-                       int K, int group, cudaStream_t stream) {
+                       int K, int group, const Opts& opts, cudaStream_t stream) {
   dim3 block(128), grid((N + 127) / 128, (M + 7) / 8);
   wq_gemm_simt<BITS><<<grid, block, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const uint8_t*>(qw),
       static_cast<const __nv_bfloat16*>(scales), static_cast<const __nv_bfloat16*>(zeros),
-      static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(out), ldo, M, N, K, group);
+      static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(out), ldo, M, N, K, group,
+      opts.relaid, opts.epilogue);
   return cudaGetLastError() == cudaSuccess ? DXB_OK : DXB_ERR_CUDA;
 }
 
@@ -1089,42 +1422,65 @@ static int check_args(int bits, const void* x, long long ldx, const void* qw, co
   return DXB_OK;
 }
 
-}  // namespace dx
+static bool pointers_aligned(int bits, const void* x, long long ldx, const void* qweight, const void* scales,
+                             const void* zeros, const void* bias, const void* out, long long ldo, int K) {
+  return (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) &&
+         (reinterpret_cast<uintptr_t>(qweight) % 16 == 0) && (reinterpret_cast<uintptr_t>(scales) % 16 == 0) &&
+         (zeros == nullptr || reinterpret_cast<uintptr_t>(zeros) % 16 == 0) &&
+         (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 8 == 0) &&
+         (reinterpret_cast<uintptr_t>(out) % 8 == 0) && (ldo % 4 == 0) && (bits != 4 || (K / 2) % 8 == 0);
+}
 
-// =================================================================== C ABI ==
-extern "C" {
+// Checks dxb_gemm_opts against the problem and copies it.
+static int read_opts(const dxb_gemm_opts* o, int bits, int M, int N, int K, Opts* out) {
+  Opts r;
+  if (o) {
+    if (o->weight_layout != DXB_LAYOUT_DEXTER && o->weight_layout != DXB_LAYOUT_B200) return DXB_ERR_UNSUPPORTED;
+    if (o->weight_layout == DXB_LAYOUT_B200 && (bits != 4 || (K / 2) % 2 || N % 4)) return DXB_ERR_UNSUPPORTED;
+    if (o->epilogue != DXB_EPILOGUE_NONE && o->epilogue != DXB_EPILOGUE_GELU_TANH) return DXB_ERR_UNSUPPORTED;
+    r.relaid = o->weight_layout == DXB_LAYOUT_B200;
+    r.epilogue = o->epilogue;
+    r.max_ctas = o->max_ctas;
+    if (o->peer_world > 1) {
+      if (o->peer_world > kPeerMaxRanks || o->peer_rank < 0 || o->peer_rank >= o->peer_world) return DXB_ERR_SHAPE;
+      if (!o->peer_regions) return DXB_ERR_NULL;
+      // one token block, whole 4-column groups, a counter per tile, room for the partial output
+      if (M > 128 || N % 4 || (N + kTileN - 1) / kTileN > kFusedMaxTiles) return DXB_ERR_UNSUPPORTED;
+      if (o->peer_capacity_elems < static_cast<int64_t>(M) * N) return DXB_ERR_SHAPE;
+      for (int i = 0; i < o->peer_world; ++i) {
+        if (!o->peer_regions[i] || reinterpret_cast<uintptr_t>(o->peer_regions[i]) % 16) return DXB_ERR_NULL;
+        r.peer.region[i] = static_cast<unsigned char*>(o->peer_regions[i]);
+      }
+      r.peer.capacity = o->peer_capacity_elems;
+      r.peer.rank = o->peer_rank;
+      r.peer.world = o->peer_world;
+      r.peer.wait_tries = wait_tries();
+    }
+  }
+  *out = r;
+  return DXB_OK;
+}
 
-#ifdef DXB_TRACE
-void dxb_debug_set_trace(void* ptr) { dx::g_trace = static_cast<long long*>(ptr); }
-#endif
-
-int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const void* scales,
-                const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
-                int group_size, void* workspace, size_t workspace_bytes, int max_ctas,
-                void* cuda_stream) {
-  using namespace dx;
-  int rc = check_args(bits, x, ldx, qweight, scales, out, ldo, M, N, K, group_size);
-  if (rc != DXB_OK) return rc;
-  if (M == 0) return DXB_OK;
-  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  const bool aligned = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (ldx % 8 == 0) &&
-                       (reinterpret_cast<uintptr_t>(qweight) % 16 == 0) &&
-                       (reinterpret_cast<uintptr_t>(scales) % 16 == 0) &&
-                       (zeros == nullptr || reinterpret_cast<uintptr_t>(zeros) % 16 == 0) &&
-                       (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 8 == 0) &&
-                       (reinterpret_cast<uintptr_t>(out) % 8 == 0) && (ldo % 4 == 0) &&
-                       (bits != 4 || (K / 2) % 8 == 0);
+static int gemm_dispatch(int bits, const void* x, int64_t ldx, const void* qweight, const void* scales,
+                         const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
+                         int group_size, void* workspace, size_t workspace_bytes, const Opts& opts,
+                         cudaStream_t stream) {
+  const int max_ctas = opts.max_ctas;
+  const bool aligned = pointers_aligned(bits, x, ldx, qweight, scales, zeros, bias, out, ldo, K);
   auto launch = [&](const char* xc, char* oc, int mc) -> int {
     if (bits == 4)
       return zeros ? launch_tc<4, true>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
-                                        group_size, workspace, workspace_bytes, max_ctas, stream)
+                                        group_size, workspace, workspace_bytes, opts, stream)
                    : launch_tc<4, false>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
-                                         group_size, workspace, workspace_bytes, max_ctas, stream);
+                                         group_size, workspace, workspace_bytes, opts, stream);
     return zeros ? launch_tc<8, true>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
-                                      group_size, workspace, workspace_bytes, max_ctas, stream)
+                                      group_size, workspace, workspace_bytes, opts, stream)
                  : launch_tc<8, false>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
-                                       group_size, workspace, workspace_bytes, max_ctas, stream);
+                                       group_size, workspace, workspace_bytes, opts, stream);
   };
+  // The sum over ranks lives in the tensor-core kernel's epilogue only.
+  if (opts.peer.world > 1 && !(aligned && gemm_tc_supported(M, N, K, group_size, bits)))
+    return DXB_ERR_UNSUPPORTED;
   // More than 128 tokens: one launch over all token blocks when the workspace holds the
   // partial sums of that plan (dxb_workspace_bytes asks for it); a smaller workspace still
   // works, block by block.
@@ -1140,17 +1496,52 @@ int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const
     const int mc = (M - m0) < chunk ? (M - m0) : chunk;
     const char* xc = static_cast<const char*>(x) + static_cast<long long>(m0) * ldx * 2;
     char* oc = static_cast<char*>(out) + static_cast<long long>(m0) * ldo * 2;
+    int rc;
     if (aligned && gemm_tc_supported(mc, N, K, group_size, bits)) {
       rc = launch(xc, oc, mc);
     } else {
       rc = bits == 4 ? launch_simt<4>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
-                                      group_size, stream)
+                                      group_size, opts, stream)
                      : launch_simt<8>(xc, ldx, qweight, scales, zeros, bias, oc, ldo, mc, N, K,
-                                      group_size, stream);
+                                      group_size, opts, stream);
     }
     if (rc != DXB_OK) return rc;
   }
   return DXB_OK;
+}
+
+}  // namespace dx
+
+// =================================================================== C ABI ==
+extern "C" {
+
+#ifdef DXB_TRACE
+void dxb_debug_set_trace(void* ptr) { dx::g_trace = static_cast<long long*>(ptr); }
+#endif
+
+int dxb_wq_gemm_ex(int bits, const void* x, int64_t ldx, const void* qweight, const void* scales,
+                   const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
+                   int group_size, void* workspace, size_t workspace_bytes, const dxb_gemm_opts* opts,
+                   void* cuda_stream) {
+  using namespace dx;
+  int rc = check_args(bits, x, ldx, qweight, scales, out, ldo, M, N, K, group_size);
+  if (rc != DXB_OK) return rc;
+  Opts o;
+  rc = read_opts(opts, bits, M, N, K, &o);
+  if (rc != DXB_OK) return rc;
+  if (M == 0) return DXB_OK;
+  return gemm_dispatch(bits, x, ldx, qweight, scales, zeros, bias, out, ldo, M, N, K, group_size, workspace,
+                       workspace_bytes, o, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const void* scales,
+                const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
+                int group_size, void* workspace, size_t workspace_bytes, int max_ctas,
+                void* cuda_stream) {
+  dxb_gemm_opts o = {};
+  o.max_ctas = max_ctas;
+  return dxb_wq_gemm_ex(bits, x, ldx, qweight, scales, zeros, bias, out, ldo, M, N, K, group_size, workspace,
+                        workspace_bytes, &o, cuda_stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -1192,21 +1583,24 @@ int dxb_wq_gemm_static(int bits, const void* x, int64_t ldx, const void* qweight
   if (rc != DXB_OK) return rc;
   if (M == 0) return DXB_OK;
   // What one launch of at most 128 tokens needs; with more tokens dxb_wq_gemm takes the
-  // one-launch plan when the array holds it and goes block by block otherwise.
-  {
-    const int rows = bits == 4 ? K / 2 : K;
-    if (rows >= (bits == 4 ? 64 : 128) &&
-        (plan_workspace_bytes(M <= 128 ? M : 128, N, K, bits, 0) > kStaticScratchBytes ||
-         (M > 128 && plan_workspace_bytes(96, N, K, bits, 0) > kStaticScratchBytes)))
-      return DXB_ERR_SCRATCH_LIMIT;
-  }
+  // one-launch plan when the array holds it and goes block by block otherwise.  Shapes that
+  // run on the plain CUDA-core kernel use no scratch at all.
+  const int mc = M <= 128 ? M : 128;
+  if (pointers_aligned(bits, x, ldx, qweight, scales, zeros, bias, out, ldo, K) &&
+      gemm_tc_supported(mc, N, K, group_size, bits) &&
+      (plan_workspace_bytes(mc, N, K, bits, 0) > kStaticScratchBytes ||
+       (M > 128 && plan_workspace_bytes(96, N, K, bits, 0) > kStaticScratchBytes)))
+    return DXB_ERR_SCRATCH_LIMIT;
   void* scratch = nullptr;
   rc = static_scratch_address(&scratch);
   if (rc != DXB_OK) return rc;
   // The array keeps whatever the previous call left.  Partial sums are always written
-  // before they are read, but the status word and the tile counters must start at zero.
+  // before they are read, but the tile counters must start at zero.  The status word in
+  // front of them is left alone: a timeout reported by an earlier call stays readable
+  // (dxb_read_status(NULL, stream)) until it has been read.
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  if (cudaMemsetAsync(scratch, 0, kStatusBytes + counters_bytes(0), stream) != cudaSuccess)
+  if (cudaMemsetAsync(static_cast<unsigned char*>(scratch) + kStatusBytes, 0, counters_bytes(0), stream) !=
+      cudaSuccess)
     return DXB_ERR_CUDA;
   return dxb_wq_gemm(bits, x, ldx, qweight, scales, zeros, bias, out, ldo, M, N, K, group_size,
                      scratch, kStaticScratchBytes, 0, cuda_stream);
@@ -1226,31 +1620,61 @@ int dxb_w8a16(const void* x, int64_t ldx, const void* qweight, const void* scale
                      workspace, workspace_bytes, 0, cuda_stream);
 }
 
-size_t dxb_workspace_bytes(int M, int N, int K, int bits) {
+size_t dxb_workspace_bytes_ex(int M, int N, int K, int bits, int max_ctas) {
   using namespace dx;
   if (M <= 0 || N <= 0 || K <= 0 || (bits != 4 && bits != 8)) return kStatusBytes;
   const int rows = bits == 4 ? K / 2 : K;
   if (rows < (bits == 4 ? 64 : 128)) return kStatusBytes;
   // Up to 128 tokens: that launch.  More: the larger of the one-launch plan over all token
   // blocks and the plan of a single block (used when the caller's workspace is smaller).
-  size_t one_block = plan_workspace_bytes(M <= 128 ? M : 128, N, K, bits, 0);
+  size_t one_block = plan_workspace_bytes(M <= 128 ? M : 128, N, K, bits, max_ctas);
   if (M <= 128) return one_block;
   // block by block, few-tile weights go in blocks of 96 tokens (see dxb_wq_gemm)
-  const size_t block96 = plan_workspace_bytes(96, N, K, bits, 0);
+  const size_t block96 = plan_workspace_bytes(96, N, K, bits, max_ctas);
   if (block96 > one_block) one_block = block96;
   if (static_cast<long long>((N + kTileN - 1) / kTileN) * ((M + 127) / 128) > kMaxTiles)
     return one_block;
-  const size_t all_blocks = plan_workspace_bytes(M, N, K, bits, 0);
+  const size_t all_blocks = plan_workspace_bytes(M, N, K, bits, max_ctas);
   return all_blocks > one_block ? all_blocks : one_block;
 }
 
-int dxb_dequantize(const void* qweight, const void* scales, const void* zeros, void* w_out, int N,
-                   int K, int group_size, int bits, void* cuda_stream) {
+size_t dxb_workspace_bytes(int M, int N, int K, int bits) { return dxb_workspace_bytes_ex(M, N, K, bits, 0); }
+
+int dxb_relayout_w4(const void* qweight, void* out, int K, int N, int inverse, void* cuda_stream) {
+  using namespace dx;
+  if (!qweight || !out) return DXB_ERR_NULL;
+  if (K <= 0 || N <= 0 || K % 4 || N % 4) return DXB_ERR_SHAPE;  // whole row pairs, whole 32-bit words
+  if (reinterpret_cast<uintptr_t>(qweight) % 4 || reinterpret_cast<uintptr_t>(out) % 4) return DXB_ERR_UNSUPPORTED;
+  const long long row_pairs = K / 4;
+  const int n4 = N / 4;
+  const long long total = row_pairs * n4;
+  const int block = 256;
+  wq_relayout_w4_kernel<<<static_cast<unsigned>((total + block - 1) / block), block, 0,
+                          static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint32_t*>(qweight), static_cast<uint32_t*>(out), row_pairs, n4, inverse ? 1 : 0);
+  return cudaGetLastError() == cudaSuccess ? DXB_OK : DXB_ERR_CUDA;
+}
+
+size_t dxb_fused_reduce_bytes(int world, int64_t capacity_elems) {
+  if (world < 1 || world > dx::kPeerMaxRanks || capacity_elems <= 0) return 0;
+  const size_t cap = (static_cast<size_t>(capacity_elems) + 7) / 8 * 8;
+  return dx::kFusedHeaderBytes + 2 * static_cast<size_t>(world) * cap * 2;
+}
+
+void dxb_set_wait_limit_ms(int ms) {
+  const long long tries = static_cast<long long>(ms < 1 ? 1 : ms) * 4000;
+  dx::g_wait_tries.store(static_cast<unsigned>(tries > 4000000000ll ? 4000000000ll : tries));
+}
+
+int dxb_dequantize_ex(const void* qweight, const void* scales, const void* zeros, void* w_out, int N,
+                      int K, int group_size, int bits, int weight_layout, void* cuda_stream) {
   using namespace dx;
   if (bits != 4 && bits != 8) return DXB_ERR_BITS;
   if (!qweight || !scales || !w_out) return DXB_ERR_NULL;
   if (N <= 0 || K <= 0 || group_size <= 0 || K % group_size || (bits == 4 && K % 2))
     return DXB_ERR_SHAPE;
+  if (weight_layout != DXB_LAYOUT_DEXTER && (weight_layout != DXB_LAYOUT_B200 || bits != 4 || K % 4 || N % 4))
+    return DXB_ERR_UNSUPPORTED;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   const long long total = static_cast<long long>(K) * N;
   const int block = 256;
@@ -1258,12 +1682,18 @@ int dxb_dequantize(const void* qweight, const void* scales, const void* zeros, v
   if (bits == 4)
     wq_dequant_kernel<4><<<grid, block, 0, stream>>>(
         static_cast<const uint8_t*>(qweight), static_cast<const __nv_bfloat16*>(scales),
-        static_cast<const __nv_bfloat16*>(zeros), static_cast<__nv_bfloat16*>(w_out), N, K, group_size);
+        static_cast<const __nv_bfloat16*>(zeros), static_cast<__nv_bfloat16*>(w_out), N, K, group_size,
+        weight_layout == DXB_LAYOUT_B200);
   else
     wq_dequant_kernel<8><<<grid, block, 0, stream>>>(
         static_cast<const uint8_t*>(qweight), static_cast<const __nv_bfloat16*>(scales),
-        static_cast<const __nv_bfloat16*>(zeros), static_cast<__nv_bfloat16*>(w_out), N, K, group_size);
+        static_cast<const __nv_bfloat16*>(zeros), static_cast<__nv_bfloat16*>(w_out), N, K, group_size, 0);
   return cudaGetLastError() == cudaSuccess ? DXB_OK : DXB_ERR_CUDA;
+}
+
+int dxb_dequantize(const void* qweight, const void* scales, const void* zeros, void* w_out, int N,
+                   int K, int group_size, int bits, void* cuda_stream) {
+  return dxb_dequantize_ex(qweight, scales, zeros, w_out, N, K, group_size, bits, DXB_LAYOUT_DEXTER, cuda_stream);
 }
 
 int dxb_uses_tensor_cores(int M, int N, int K, int group_size, int bits) {
@@ -1272,11 +1702,14 @@ int dxb_uses_tensor_cores(int M, int N, int K, int group_size, int bits) {
 }
 
 int dxb_read_status(void* workspace, void* cuda_stream) {
-  if (!workspace) return DXB_ERR_NULL;
-  int code = 0;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  const bool builtin = workspace == nullptr;  // the scratch of dxb_wq_gemm_static
+  if (builtin && dx::static_scratch_address(&workspace) != DXB_OK) return DXB_ERR_CUDA;
+  int code = 0;
   if (cudaMemcpyAsync(&code, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess)
     return DXB_ERR_CUDA;
+  // The built-in scratch has no owner who could clear its status word: reading it does.
+  if (builtin && cudaMemsetAsync(workspace, 0, sizeof(int), stream) != cudaSuccess) return DXB_ERR_CUDA;
   if (cudaStreamSynchronize(stream) != cudaSuccess) return DXB_ERR_CUDA;
   return code;
 }
@@ -1287,7 +1720,7 @@ const char* dxb_strerror(int code) {
     case DXB_ERR_BITS: return "bits must be 4 or 8";
     case DXB_ERR_NULL: return "null pointer argument";
     case DXB_ERR_SHAPE: return "inconsistent shape, stride or group size";
-    case DXB_ERR_UNSUPPORTED: return "shape not supported by this build";
+    case DXB_ERR_UNSUPPORTED: return "shape or option not supported by this build";
     case DXB_ERR_WORKSPACE: return "workspace missing or too small (see dxb_workspace_bytes)";
     case DXB_ERR_TENSORMAP: return "could not encode a TMA tensor map";
     case DXB_ERR_CUDA: return "CUDA launch or runtime error";

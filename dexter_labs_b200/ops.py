@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import weakref
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -21,8 +22,9 @@ from . import _lib
 from .platform import ArchVersion, Capability
 from .registry import Priority, register, select
 
-__all__ = ["w4a16", "w8a16", "linear", "dequantize", "accepts", "KERNEL_NAMES", "register_with",
-           "last_status", "chain", "chain_status", "ChainLink", "CHAIN_MAX", "PeerAllReduce"]
+__all__ = ["w4a16", "w8a16", "w4a16_gelu", "w8a16_gelu", "linear", "dequantize", "accepts", "KERNEL_NAMES",
+           "register_with", "last_status", "PeerAllReduce",
+           "FusedReduce", "relayout_w4", "prepared_w4", "set_wait_limit_ms"]
 
 KERNEL_NAMES = {"w4a16": "b200_w4a16_tcgen05", "w8a16": "b200_w8a16_tcgen05"}
 
@@ -53,9 +55,19 @@ def _raise(code: int) -> None:
     raise RuntimeError(text)
 
 
+_LAYOUTS = {"dexter": _lib.LAYOUT_DEXTER, "b200": _lib.LAYOUT_B200}
+_EPILOGUES = {None: _lib.EPILOGUE_NONE, "gelu_tanh": _lib.EPILOGUE_GELU_TANH}
+_need_cache: Dict[Tuple[int, int, int, int, int], int] = {}  # workspace bytes per problem
+
+
+def _raw_stream(device_index: int) -> int:
+    return torch._C._cuda_getCurrentRawStream(device_index)
+
+
 def _run(bits: int, x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
          zeros: Optional[torch.Tensor], bias: Optional[torch.Tensor], group_size: int,
-         max_ctas: int = 0) -> torch.Tensor:
+         max_ctas: int = 0, *, layout: str = "dexter", epilogue: Optional[str] = None,
+         reduce: Optional["FusedReduce"] = None) -> torch.Tensor:
     if not x.is_cuda:
         raise RuntimeError("the B200 backend needs CUDA tensors; there is no CPU path")
     if x.dtype != torch.bfloat16 or scales.dtype != torch.bfloat16:
@@ -67,7 +79,10 @@ def _run(bits: int, x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor
     if k_in != k_dim:
         raise ValueError(f"x has K={k_in} but the packed weight has K={k_dim}")
     n = qweight.shape[1]
-    qweight = qweight if qweight.is_contiguous() else qweight.contiguous()
+    if not qweight.is_contiguous():
+        if layout != "dexter":
+            raise ValueError("a re-laid-out weight must be contiguous")
+        qweight = qweight.contiguous()
     scales = scales if scales.is_contiguous() else scales.contiguous()
     if zeros is not None and not zeros.is_contiguous():
         zeros = zeros.contiguous()
@@ -82,22 +97,95 @@ def _run(bits: int, x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor
     if m == 0:
         return out.view(*lead, n)
 
-    with torch.cuda.device(x.device):
-        stream = torch.cuda.current_stream().cuda_stream
-        need = _LIB.dxb_workspace_bytes(m, n, k_dim, bits)
-        ws = _workspace(x.device, stream, need)
-        rc = _LIB.dxb_wq_gemm(bits, x2.data_ptr(), x2.stride(0), qweight.data_ptr(),
-                              scales.data_ptr(), _ptr(zeros), _ptr(bias), out.data_ptr(), n, m, n,
-                              k_dim, group_size, ws.data_ptr(), ws.numel(), max_ctas,
-                              ctypes.c_void_p(stream))
-        if rc != _lib.OK:
-            _raise(rc)
-        if os.environ.get("DEXTER_B200_CHECK"):
-            code = _LIB.dxb_read_status(ws.data_ptr(), ctypes.c_void_p(stream))
-            if code != _lib.OK:
-                ws.zero_()
-                _raise(code)
+    dev = x.device.index
+    if dev != torch.cuda.current_device():
+        with torch.cuda.device(dev):
+            return _run(bits, x, qweight, scales, zeros, bias, group_size, max_ctas, layout=layout,
+                        epilogue=epilogue, reduce=reduce)
+    if layout == "dexter" and bits == 4:
+        # load-time repack, cached per weight tensor (see prepared_w4)
+        relaid = prepared_w4(qweight, m, n, k_dim, group_size)
+        if relaid is not None:
+            qweight, layout = relaid, "b200"
+    stream = _raw_stream(dev)
+    key = (m, n, k_dim, bits, max_ctas)
+    need = _need_cache.get(key)
+    if need is None:
+        need = _need_cache[key] = _LIB.dxb_workspace_bytes_ex(m, n, k_dim, bits, max_ctas)
+    ws = _workspace(x.device, stream, need)
+    opts = _lib.GemmOpts(_LAYOUTS[layout], _EPILOGUES[epilogue], max_ctas, 0, 0, None, 0)
+    if reduce is not None:
+        opts.peer_world, opts.peer_rank = reduce.world, reduce.rank
+        opts.peer_regions, opts.peer_capacity_elems = reduce._ptrs, reduce.capacity
+    rc = _LIB.dxb_wq_gemm_ex(bits, x2.data_ptr(), x2.stride(0), qweight.data_ptr(), scales.data_ptr(),
+                             _ptr(zeros), _ptr(bias), out.data_ptr(), n, m, n, k_dim, group_size,
+                             ws.data_ptr(), ws.numel(), ctypes.byref(opts), ctypes.c_void_p(stream))
+    if rc != _lib.OK:
+        _raise(rc)
+    if _CHECK:
+        code = _LIB.dxb_read_status(ws.data_ptr(), ctypes.c_void_p(stream))
+        if code != _lib.OK:
+            ws.zero_()
+            _raise(code)
     return out.view(*lead, n)
+
+
+_CHECK = bool(os.environ.get("DEXTER_B200_CHECK"))
+
+# ------------------------------------------------------------ load-time re-layout (int4)
+# id(qweight) -> (weak reference to it, its version counter, the repacked copy)
+_relaid: Dict[int, Tuple[object, int, torch.Tensor]] = {}
+_AUTO_RELAYOUT = os.environ.get("DEXTER_B200_RELAYOUT", "1") != "0"
+
+
+def relayout_w4(qweight: torch.Tensor, *, inverse: bool = False,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Repack an int4 ``qweight`` ``[K/2, N]`` for the tensor-core kernel (``layout="b200"``).
+
+    The reference names this as its own next step ("pack into int32 words",
+    ``README.md:147-150`` there): inside every block of 2 packed rows x 4 columns the
+    nibbles are regrouped so that a 32-bit word holds, for four columns, the two values
+    of consecutive k the tensor-core operand pairs up.  Same shape; ``inverse=True`` gives
+    the reference layout back bit for bit; ``out`` may be ``qweight`` itself.
+    """
+    if qweight.dtype != torch.uint8 or qweight.ndim != 2 or not qweight.is_cuda:
+        raise ValueError("relayout_w4 takes a 2-D uint8 CUDA tensor")
+    rows, n = qweight.shape
+    if rows % 2 or n % 4:
+        raise ValueError("relayout_w4 needs an even number of packed rows and N % 4 == 0")
+    src = qweight if qweight.is_contiguous() else qweight.contiguous()
+    dst = torch.empty_like(src) if out is None else out
+    if dst.shape != src.shape or not dst.is_contiguous() or dst.dtype != torch.uint8:
+        raise ValueError("out must be a contiguous uint8 tensor of the same shape")
+    with torch.cuda.device(qweight.device):
+        stream = _raw_stream(qweight.device.index)
+        rc = _LIB.dxb_relayout_w4(src.data_ptr(), dst.data_ptr(), 2 * rows, n, 1 if inverse else 0,
+                                  ctypes.c_void_p(stream))
+    if rc != _lib.OK:
+        _raise(rc)
+    return dst
+
+
+def prepared_w4(qweight: torch.Tensor, m: int, n: int, k_dim: int, group_size: int) -> Optional[torch.Tensor]:
+    """The cached repacked copy of ``qweight`` for calls that come in with the reference
+    layout (the registered kernels), or None where the repack does not apply: shapes the
+    plain CUDA-core kernel serves, a stream that is being captured before the copy exists,
+    ``DEXTER_B200_RELAYOUT=0``.  The copy is made on the first call with a given tensor
+    object and dropped when that tensor is freed or modified in place."""
+    if not _AUTO_RELAYOUT:
+        return None
+    key = id(qweight)
+    hit = _relaid.get(key)
+    if hit is not None and hit[0]() is qweight and hit[1] == qweight._version:
+        return hit[2]
+    if (qweight.shape[0] % 2 or n % 4 or qweight.data_ptr() % 16
+            or not _LIB.dxb_uses_tensor_cores(m, n, k_dim, group_size, 4)
+            or torch.cuda.is_current_stream_capturing()):
+        return None
+    relaid = relayout_w4(qweight)
+    _relaid[key] = (weakref.ref(qweight, lambda _r, key=key: _relaid.pop(key, None)),
+                    qweight._version, relaid)
+    return relaid
 
 
 def last_status(device: Optional[torch.device] = None) -> int:
@@ -124,124 +212,39 @@ def accepts(*args) -> bool:
                 and qweight.dtype == torch.uint8 and qweight.ndim == 2 and scales.ndim == 2)
 
 
-def w4a16(x, qweight, scales, zeros, bias, group_size, *, max_ctas: int = 0):
+def w4a16(x, qweight, scales, zeros, bias, group_size, *, max_ctas: int = 0, layout: str = "dexter",
+          epilogue: Optional[str] = None, reduce: Optional["FusedReduce"] = None):
     """int4 weight-only GEMM, bf16 in / bf16 out.
 
-    ``max_ctas`` (an extension, not part of the reference signature) caps the SMs the
-    launch may use, for callers that run independent GEMMs on parallel streams.
+    Extensions beyond the reference's kernel-slot signature, all keyword-only:
+    ``max_ctas`` caps the SMs the launch may use, for callers that run independent GEMMs
+    on parallel streams; ``layout="b200"`` says ``qweight`` already went through
+    :func:`relayout_w4` (with the default the repack is made once and cached);
+    ``epilogue="gelu_tanh"`` applies the tanh-GELU of the FFN to the result;
+    ``reduce`` (a :class:`FusedReduce`) makes the call one rank's K-shard of a
+    row-parallel linear and returns the sum over ranks.
     """
-    return _run(4, x, qweight, scales, zeros, bias, group_size, max_ctas)
+    return _run(4, x, qweight, scales, zeros, bias, group_size, max_ctas, layout=layout,
+                epilogue=epilogue, reduce=reduce)
 
 
-def w8a16(x, qweight, scales, zeros, bias, group_size, *, max_ctas: int = 0):
-    """int8 weight-only GEMM, bf16 in / bf16 out (``max_ctas``: see :func:`w4a16`)."""
-    return _run(8, x, qweight, scales, zeros, bias, group_size, max_ctas)
+def w8a16(x, qweight, scales, zeros, bias, group_size, *, max_ctas: int = 0,
+          epilogue: Optional[str] = None, reduce: Optional["FusedReduce"] = None):
+    """int8 weight-only GEMM, bf16 in / bf16 out (keywords: see :func:`w4a16`)."""
+    return _run(8, x, qweight, scales, zeros, bias, group_size, max_ctas, epilogue=epilogue,
+                reduce=reduce)
 
 
-CHAIN_MAX = _lib.DXB_CHAIN_MAX
+def w4a16_gelu(x, qweight, scales, zeros, bias, group_size):
+    """``gelu_tanh(w4a16(x, ...))`` in one launch: the FFN up-projection with the activation
+    the reference applies between its packed FFN linears
+    (``python/dexter/models/dreamzero/model.py:279-285``) in the GEMM epilogue."""
+    return _run(4, x, qweight, scales, zeros, bias, group_size, epilogue="gelu_tanh")
 
 
-class ChainLink:
-    """One GEMM of a :func:`chain`: the kernel-slot arguments plus where ``x`` comes from.
-
-    ``x`` is either a tensor that is ready before the call, or the integer index of an
-    EARLIER link whose output is this link's activations.
-    """
-
-    __slots__ = ("x", "qweight", "scales", "zeros", "bias", "group_size")
-
-    def __init__(self, x, qweight, scales, zeros=None, bias=None, group_size=128):
-        self.x, self.qweight, self.scales = x, qweight, scales
-        self.zeros, self.bias, self.group_size = zeros, bias, group_size
-
-
-# One chain workspace per (device, stream): zero-filled when created; the kernel leaves it clean.
-_chain_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
-
-
-def chain(links, *, bits: int = 4, max_ctas: int = 0):
-    """Run a list of quantised GEMMs (at most ``CHAIN_MAX``) as ONE launch.
-
-    Each link computes what ``w4a16`` / ``w8a16`` would; links are started in list order
-    by one persistent grid, and a link whose ``x`` is an index waits in the kernel for
-    that link's output instead of for a kernel boundary.  Returns the list of outputs.
-    All links need at most 128 token rows and shapes the tensor-core kernel takes;
-    otherwise the library refuses (``RuntimeError``) and the caller should issue the
-    GEMMs one by one.
-    """
-    if bits not in (4, 8):
-        raise ValueError(f"weight-only quantisation supports 4 or 8 bits, got {bits}")
-    links = list(links)
-    if not 1 <= len(links) <= CHAIN_MAX:
-        raise ValueError(f"a chain holds 1..{CHAIN_MAX} GEMMs, got {len(links)}")
-    items = (_lib.ChainItem * len(links))()
-    outs, keep = [], []
-    device = links[0].qweight.device
-    if device.type != "cuda":
-        raise RuntimeError("the B200 backend needs CUDA tensors; there is no CPU path")
-    for i, ln in enumerate(links):
-        k_dim = ln.qweight.shape[0] * (2 if bits == 4 else 1)
-        n = ln.qweight.shape[1]
-        if isinstance(ln.x, int):
-            if not 0 <= ln.x < i:
-                raise ValueError(f"link {i} depends on link {ln.x}, which does not come before it")
-            x2, dep = outs[ln.x], ln.x
-        else:
-            x2, dep = ln.x.reshape(-1, ln.x.shape[-1]), -1
-            if x2.dtype != torch.bfloat16:
-                raise RuntimeError("the B200 backend computes bf16 activations only")
-            if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
-                x2 = x2.contiguous()
-        if x2.shape[1] != k_dim:
-            raise ValueError(f"link {i}: x has K={x2.shape[1]} but the packed weight has K={k_dim}")
-        if ln.qweight.dtype != torch.uint8 or ln.scales.dtype != torch.bfloat16:
-            raise ValueError("packed weights must be uint8 with bf16 scales")
-        qweight, scales = ln.qweight.contiguous(), ln.scales.contiguous()
-        zeros = None if ln.zeros is None else ln.zeros.contiguous()
-        bias = None if ln.bias is None else ln.bias.contiguous()
-        m = x2.shape[0]
-        out = torch.empty((m, n), device=device, dtype=torch.bfloat16)
-        keep.append((x2, qweight, scales, zeros, bias))
-        outs.append(out)
-        it = items[i]
-        it.x, it.ldx = x2.data_ptr(), x2.stride(0)
-        it.qweight, it.scales = qweight.data_ptr(), scales.data_ptr()
-        it.zeros, it.bias = _ptr(zeros), _ptr(bias)
-        it.out, it.ldo = out.data_ptr(), n
-        it.M, it.N, it.K, it.group_size = m, n, k_dim, ln.group_size
-        it.depends_on = dep
-    with torch.cuda.device(device):
-        stream = torch.cuda.current_stream().cuda_stream
-        need = _LIB.dxb_chain_workspace_bytes(bits, items, len(links), max_ctas)
-        if need == 0:
-            # let the launch call report why
-            need = 256
-        key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
-        ws = _chain_workspaces.get(key)
-        if ws is None or ws.numel() < need:
-            ws = torch.zeros(max(need, 256), dtype=torch.uint8, device=device)
-            _chain_workspaces[key] = ws
-        rc = _LIB.dxb_wq_gemm_chain(bits, items, len(links), ws.data_ptr(), ws.numel(), max_ctas,
-                                    ctypes.c_void_p(stream))
-        if rc != _lib.OK:
-            _raise(rc)
-        if os.environ.get("DEXTER_B200_CHECK"):
-            code = _LIB.dxb_read_status(ws.data_ptr(), ctypes.c_void_p(stream))
-            if code != _lib.OK:
-                ws.zero_()
-                _raise(code)
-    return outs
-
-
-def chain_status(device: Optional[torch.device] = None) -> int:
-    """Synchronise and return the status word of the current stream's chain workspace."""
-    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
-    with torch.cuda.device(device):
-        stream = torch.cuda.current_stream().cuda_stream
-        ws = _chain_workspaces.get((device.index, stream))
-        if ws is None:
-            return _lib.OK
-        return _LIB.dxb_read_status(ws.data_ptr(), ctypes.c_void_p(stream))
+def w8a16_gelu(x, qweight, scales, zeros, bias, group_size):
+    """int8 counterpart of :func:`w4a16_gelu`."""
+    return _run(8, x, qweight, scales, zeros, bias, group_size, epilogue="gelu_tanh")
 
 
 class PeerAllReduce:
@@ -300,12 +303,50 @@ class PeerAllReduce:
         return int(self.status.item())
 
 
+class FusedReduce:
+    """Peer-mapped memory for the sum over ranks that ``w4a16(..., reduce=...)`` fuses into a
+    row-parallel GEMM (``dxb_wq_gemm_ex`` with ``peer_*`` options).
+
+    Built once per process group (a collective: every rank constructs it at the same point):
+    allocates this rank's region through ``torch.distributed._symmetric_memory``, zero-fills
+    it and exchanges the mappings.  Every rank then makes the same sequence of
+    ``reduce=``-calls with the same M and N (at most 128 tokens, ``M * N <= capacity``),
+    passes the FULL bias, and gets the full result.
+    """
+
+    def __init__(self, group, capacity_elems: int, device: torch.device) -> None:
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.capacity = (int(capacity_elems) + 7) // 8 * 8
+        nbytes = _LIB.dxb_fused_reduce_bytes(self.world, self.capacity)
+        if nbytes == 0:
+            raise RuntimeError("the fused sum over ranks supports at most 8 ranks")
+        # plain peer mappings are all the kernel uses: keep the region off NVLink multicast
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        with torch.cuda.device(device):
+            self.region = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+            self.region.zero_()
+            self.handle = symm_mem.rendezvous(self.region, group.group_name)
+            torch.cuda.synchronize()
+        dist.barrier(group)  # every region is zero before anyone's first call
+        self._ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self.handle.buffer_ptrs])
+
+
+def set_wait_limit_ms(ms: int) -> None:
+    """Upper bound of a kernel's wait for another GPU (``dxb_set_wait_limit_ms``)."""
+    _LIB.dxb_set_wait_limit_ms(int(ms))
+
+
 def dequantize(qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torch.Tensor],
-               group_size: int, bits: int) -> torch.Tensor:
+               group_size: int, bits: int, *, layout: str = "dexter") -> torch.Tensor:
     """Dense ``[K, N]`` bf16 weight from the CUDA kernel's own arithmetic.
 
     Counterpart of the reference's ``dequantize`` (``reference/gemm.py:51-73``);
-    exists so the dequantisation can be compared bit for bit.
+    exists so the dequantisation can be compared bit for bit.  ``layout="b200"``:
+    ``qweight`` went through :func:`relayout_w4`.
     """
     if bits not in (4, 8):
         raise ValueError(f"weight-only quantisation supports 4 or 8 bits, got {bits}")
@@ -316,10 +357,10 @@ def dequantize(qweight: torch.Tensor, scales: torch.Tensor, zeros: Optional[torc
     out = torch.empty((k_dim, n), device=qweight.device, dtype=torch.bfloat16)
     with torch.cuda.device(qweight.device):
         stream = torch.cuda.current_stream().cuda_stream
-        rc = _LIB.dxb_dequantize(qweight.contiguous().data_ptr(), scales.contiguous().data_ptr(),
-                                 None if zeros is None else zeros.contiguous().data_ptr(),
-                                 out.data_ptr(), n, k_dim, group_size, bits,
-                                 ctypes.c_void_p(stream))
+        rc = _LIB.dxb_dequantize_ex(qweight.contiguous().data_ptr(), scales.contiguous().data_ptr(),
+                                    None if zeros is None else zeros.contiguous().data_ptr(),
+                                    out.data_ptr(), n, k_dim, group_size, bits, _LAYOUTS[layout],
+                                    ctypes.c_void_p(stream))
     if rc != _lib.OK:
         _raise(rc)
     return out

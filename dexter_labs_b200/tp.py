@@ -117,6 +117,8 @@ class ShardedLinear:
     weight: QuantizedWeight
     k_range: Tuple[int, int]  # activation columns this rank consumes
     full_shape: Tuple[int, int]  # unsharded (K, N)
+    layout: str = "dexter"       # "b200" once the packed int4 bytes went through ops.relayout_w4
+    full_bias: Optional[torch.Tensor] = None  # row-parallel: the linear's bias on EVERY rank
 
     @property
     def weight_bytes(self) -> int:
@@ -127,11 +129,15 @@ class ShardedLinear:
         return 2 * m * k * n
 
 
-def _default_gemm(x: torch.Tensor, w: QuantizedWeight, max_ctas: int = 0) -> torch.Tensor:
+def _default_gemm(x: torch.Tensor, w: QuantizedWeight, max_ctas: int = 0, *, layout: str = "dexter",
+                  reduce=None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     from . import ops
 
-    fn = ops.w4a16 if w.bits == 4 else ops.w8a16
-    return fn(x, w.qweight, w.scales, w.zeros, w.bias, w.group_size, max_ctas=max_ctas)
+    bias = w.bias if bias is None else bias
+    if w.bits == 4:
+        return ops.w4a16(x, w.qweight, w.scales, w.zeros, bias, w.group_size, max_ctas=max_ctas,
+                         layout=layout, reduce=reduce)
+    return ops.w8a16(x, w.qweight, w.scales, w.zeros, bias, w.group_size, max_ctas=max_ctas, reduce=reduce)
 
 
 # (name, input, kind): the ten linears of one DiT block in execution order
@@ -162,7 +168,8 @@ class LayerSet:
     world: int = 1
     bits: int = 4
     group_size: int = 128
-    collective: str = "rs_ag"  # "rs_ag" | "all_reduce" | "peer" (own kernel over peer memory)
+    collective: str = "rs_ag"  # "rs_ag" | "all_reduce" (NCCL) | "peer" (own all-reduce kernel over peer
+                               # memory) | "fused" (the sum is part of the row-parallel GEMM's launch)
     fuse_qkv: bool = False     # one launch for self q,k,v and one for cross k,v (N-concatenation)
     concurrent: bool = False   # independent linears of a block on parallel CUDA streams
     layers: List[List[ShardedLinear]] = field(default_factory=list)
@@ -172,6 +179,8 @@ class LayerSet:
     _side: Optional[list] = None
     _sms: int = 0
     _peer: Optional[object] = None  # ops.PeerAllReduce, see enable_peer_reduce
+    _fused: Optional[object] = None  # ops.FusedReduce, see enable_fused_reduce
+    _plain: Dict[int, QuantizedWeight] = field(default_factory=dict)  # see _g
 
     def enable_peer_reduce(self, tokens: int, device) -> bool:
         """Set up the peer-memory all-reduce for outputs of up to ``tokens x dim`` bf16.
@@ -200,13 +209,53 @@ class LayerSet:
         self.collective = "all_reduce"
         return False
 
+    def enable_fused_reduce(self, tokens: int, device) -> bool:
+        """Set up the sum over ranks INSIDE the row-parallel GEMMs (``collective="fused"``) for
+        outputs of up to ``tokens x dim`` bf16, at most 128 tokens.  A collective: every rank
+        calls it at the same point.  Returns False (nothing changes) when peer-mapped memory
+        cannot be set up on every rank."""
+        import torch.distributed as dist
+
+        from . import ops
+
+        group = self.process_group if self.process_group is not None else dist.group.WORLD
+        ctx, ok = None, 1
+        try:
+            if tokens > 128:
+                raise ValueError("the fused sum over ranks takes at most 128 tokens")
+            ctx = ops.FusedReduce(group, tokens * self.dim, torch.device(device))
+        except Exception as exc:  # noqa: BLE001 - reported below, every rank must agree
+            ok = 0
+            self._peer_error = repr(exc)
+        flag = torch.tensor([ok], device=device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if int(flag.item()) == 1:
+            self._fused = ctx
+            self.collective = "fused"
+            return True
+        return False
+
+    def relayout_(self) -> "LayerSet":
+        """Load-time repack of every int4 weight of the set for the tensor-core kernel, in
+        place (``ops.relayout_w4``); shapes that kernel does not take keep the reference layout."""
+        from . import ops
+
+        for row in self.layers:
+            for l in row:
+                q = l.weight.qweight
+                if (l.layout == "dexter" and l.weight.bits == 4 and q.is_cuda and q.shape[0] % 64 == 0
+                        and q.shape[1] % 16 == 0 and l.weight.group_size % 64 == 0 and q.is_contiguous()):
+                    ops.relayout_w4(q, out=q)
+                    l.layout = "b200"
+        return self
+
     # ------------------------------------------------------------------ build
     @classmethod
     def build(cls, preset: str, *, blocks: Optional[int] = None, rank: int = 0, world: int = 1,
               bits: int = 4, group_size: int = 128, symmetric: bool = True, bias: bool = True,
               device="cuda", seed: int = 0, collective: str = "rs_ag", gemm: GemmFn = _default_gemm,
               process_group=None, weight_std: float = 0.02, fuse_qkv: bool = False,
-              concurrent: bool = False) -> "LayerSet":
+              concurrent: bool = False, relayout: bool = True) -> "LayerSet":
         dim, ffn, nblocks = PRESETS[preset]
         nblocks = blocks if blocks is not None else nblocks
         self = cls(dim=dim, ffn_dim=ffn, blocks=nblocks, rank=rank, world=world, bits=bits,
@@ -227,6 +276,8 @@ class LayerSet:
             if fuse_qkv:
                 row = self._fuse(row)
             self.layers.append(row)
+        if relayout and gemm is _default_gemm and str(device).startswith("cuda"):
+            self.relayout_()
         return self
 
     @staticmethod
@@ -241,8 +292,10 @@ class LayerSet:
             parts = [by[f"self_{c}"] for c in "qkv"] if name == "self_qkv" else [by["cross_k"], by["cross_v"]]
             fused = concat_columns([p.weight for p in parts])
             k = parts[0].full_shape[0]
+            if len({p.layout for p in parts}) != 1:
+                raise ValueError("only weights in the same layout concatenate")
             out.append(ShardedLinear(name, "column", fused, (0, k),
-                                     (k, sum(p.full_shape[1] for p in parts))))
+                                     (k, sum(p.full_shape[1] for p in parts)), layout=parts[0].layout))
         return out
 
     def shard(self, name: str, kind: str, full: QuantizedWeight) -> ShardedLinear:
@@ -252,7 +305,7 @@ class LayerSet:
         if kind == "column":
             return ShardedLinear(name, kind, split_columns(full, self.rank, self.world), (0, k), (k, n))
         part, k_range = split_rows(full, self.rank, self.world)
-        return ShardedLinear(name, kind, part, k_range, (k, n))
+        return ShardedLinear(name, kind, part, k_range, (k, n), full_bias=full.bias)
 
     # ------------------------------------------------------------------ stats
     @property
@@ -273,6 +326,34 @@ class LayerSet:
         return sum(l.flops(m) for r in self.layers for l in r)
 
     # ---------------------------------------------------------------- forward
+    def _g(self, x: torch.Tensor, layer: ShardedLinear, max_ctas: int = 0) -> torch.Tensor:
+        """One linear of the set on this rank (a partial product for a row-parallel one)."""
+        if self.gemm is _default_gemm:
+            return _default_gemm(x, layer.weight, max_ctas, layout=layer.layout)
+        w = layer.weight
+        if layer.layout != "dexter":
+            # a caller-supplied GEMM (the CPU oracle in tests) reads the reference layout
+            w = self._plain.get(id(layer))
+            if w is None:
+                from . import ops
+
+                q = ops.relayout_w4(layer.weight.qweight, inverse=True)
+                w = QuantizedWeight(q, layer.weight.scales, layer.weight.zeros, layer.weight.bias,
+                                    layer.weight.group_size, layer.weight.bits, layer.weight.shape)
+                self._plain[id(layer)] = w
+        return self.gemm(x, w)
+
+    def _row(self, col_out: torch.Tensor, layer: ShardedLinear) -> torch.Tensor:
+        """A row-parallel linear including the sum over ranks: one launch when the sum is fused
+        into the GEMM, else the GEMM followed by the collective."""
+        xin = self._row_input(col_out, layer)
+        if (self.world > 1 and self.collective == "fused" and self._fused is not None
+                and self.gemm is _default_gemm and xin.shape[0] <= 128
+                and xin.shape[0] * layer.full_shape[1] <= self._fused.capacity):
+            return _default_gemm(xin, layer.weight, 0, layout=layer.layout, reduce=self._fused,
+                                 bias=layer.full_bias)
+        return self._reduce(self._g(xin, layer))
+
     def _reduce(self, partial: torch.Tensor) -> torch.Tensor:
         """Sum the row-parallel partial products over ranks; every rank gets the full result."""
         if self.world == 1:
@@ -315,7 +396,7 @@ class LayerSet:
         to a fifth of the SMs; o waits for q, k, v; cross o waits for cross q, k, v.  Under
         CUDA-graph capture this becomes a fork/join graph."""
         L = {l.name: l for l in self.layers[blk]}
-        g = self.gemm
+        g = self._g
         cur = torch.cuda.current_stream()
         if self._side is None:
             self._side = [torch.cuda.Stream() for _ in range(4)]
@@ -329,17 +410,17 @@ class LayerSet:
         outs = {}
         for s, (name, inp) in zip(side, (("self_q", x), ("self_k", x), ("cross_k", ctx), ("cross_v", ctx))):
             with torch.cuda.stream(s):
-                outs[name] = g(inp, L[name].weight, share)
-        v = g(x, L["self_v"].weight, share)
+                outs[name] = g(inp, L[name], share)
+        v = g(x, L["self_v"], share)
         cur.wait_stream(side[0])
         cur.wait_stream(side[1])
-        x = self._reduce(g(self._row_input(v, L["self_o"]), L["self_o"].weight))
-        g(x, L["cross_q"].weight)
+        x = self._row(v, L["self_o"])
+        g(x, L["cross_q"])
         cur.wait_stream(side[2])
         cur.wait_stream(side[3])
-        x = self._reduce(g(self._row_input(outs["cross_v"], L["cross_o"]), L["cross_o"].weight))
-        h = g(x, L["ffn_up"].weight)
-        x = self._reduce(g(self._row_input(h, L["ffn_down"]), L["ffn_down"].weight))
+        x = self._row(outs["cross_v"], L["cross_o"])
+        h = g(x, L["ffn_up"])
+        x = self._row(h, L["ffn_down"])
         return x
 
     def _block_forward_overlapped(self, L, x: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
@@ -347,7 +428,7 @@ class LayerSet:
         GPU would otherwise wait for NVLink, so cross k and cross v (which only need the
         context) are held back until self o's GEMM has been issued and then run on two side
         streams while that collective is in flight on the main stream."""
-        g = self.gemm
+        g = self._g
         cur = torch.cuda.current_stream()
         side = self._side
         third = max(self._sms // 3, 1)
@@ -356,23 +437,33 @@ class LayerSet:
             s.wait_stream(cur)
         for s, name in zip(side[:2], ("self_q", "self_k")):
             with torch.cuda.stream(s):
-                g(x, L[name].weight, third)
-        v = g(x, L["self_v"].weight, third)
+                g(x, L[name], third)
+        v = g(x, L["self_v"], third)
         cur.wait_stream(side[0])
         cur.wait_stream(side[1])
-        partial = g(self._row_input(v, L["self_o"]), L["self_o"].weight)
         outs = {}
-        for s, name in zip(side[2:], ("cross_k", "cross_v")):
-            s.wait_stream(cur)  # after self o's GEMM, alongside its collective
-            with torch.cuda.stream(s):
-                outs[name] = g(ctx, L[name].weight, half)
-        x = self._reduce(partial)
-        g(x, L["cross_q"].weight)
+        if self.collective == "fused":
+            # the sum is inside self o's launch: fork before it, so cross k and cross v run
+            # beside it and fill the SMs while it waits for the other ranks
+            for s in side[2:]:
+                s.wait_stream(cur)
+            x = self._row(v, L["self_o"])
+            for s, name in zip(side[2:], ("cross_k", "cross_v")):
+                with torch.cuda.stream(s):
+                    outs[name] = g(ctx, L[name], half)
+        else:
+            partial = g(self._row_input(v, L["self_o"]), L["self_o"])
+            for s, name in zip(side[2:], ("cross_k", "cross_v")):
+                s.wait_stream(cur)  # after self o's GEMM, alongside its collective
+                with torch.cuda.stream(s):
+                    outs[name] = g(ctx, L[name], half)
+            x = self._reduce(partial)
+        g(x, L["cross_q"])
         cur.wait_stream(side[2])
         cur.wait_stream(side[3])
-        x = self._reduce(g(self._row_input(outs["cross_v"], L["cross_o"]), L["cross_o"].weight))
-        h = g(x, L["ffn_up"].weight)
-        x = self._reduce(g(self._row_input(h, L["ffn_down"]), L["ffn_down"].weight))
+        x = self._row(outs["cross_v"], L["cross_o"])
+        h = g(x, L["ffn_up"])
+        x = self._row(h, L["ffn_down"])
         return x
 
     def _block_forward_fused_overlapped(self, blk: int, x: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
@@ -382,7 +473,7 @@ class LayerSet:
         back until self o's GEMM has been issued and runs while that GEMM's collective is in
         flight on the main stream."""
         L = {l.name: l for l in self.layers[blk]}
-        g = self.gemm
+        g = self._g
         cur = torch.cuda.current_stream()
         if self._side is None:
             self._side = [torch.cuda.Stream() for _ in range(4)]
@@ -393,24 +484,33 @@ class LayerSet:
             kv_share = max(min(kv_tiles, self._sms // 3), 1)
             side.wait_stream(cur)
             with torch.cuda.stream(side):
-                kv = g(ctx, L["cross_kv"].weight, kv_share)
-            qkv = g(x, L["self_qkv"].weight, self._sms - kv_share)
+                kv = g(ctx, L["cross_kv"], kv_share)
+            qkv = g(x, L["self_qkv"], self._sms - kv_share)
             v = qkv[:, 2 * (qkv.shape[1] // 3):]
-            partial = g(self._row_input(v, L["self_o"]), L["self_o"].weight)
+            x = self._row(v, L["self_o"])
+        elif self.collective == "fused":
+            # the sum is inside self o's launch: fork before it, so the cross k/v launch runs
+            # beside it and fills the SMs while it waits for the other ranks
+            qkv = g(x, L["self_qkv"])
+            v = qkv[:, 2 * (qkv.shape[1] // 3):]
+            side.wait_stream(cur)
+            x = self._row(v, L["self_o"])
+            with torch.cuda.stream(side):
+                kv = g(ctx, L["cross_kv"], max(self._sms // 2, 1))
         else:
-            qkv = g(x, L["self_qkv"].weight)
+            qkv = g(x, L["self_qkv"])
             v = qkv[:, 2 * (qkv.shape[1] // 3):]
-            partial = g(self._row_input(v, L["self_o"]), L["self_o"].weight)
+            partial = g(self._row_input(v, L["self_o"]), L["self_o"])
             side.wait_stream(cur)  # after self o's GEMM, alongside its collective
             with torch.cuda.stream(side):
-                kv = g(ctx, L["cross_kv"].weight, max(self._sms // 2, 1))
-        x = self._reduce(partial)
-        g(x, L["cross_q"].weight)
+                kv = g(ctx, L["cross_kv"], max(self._sms // 2, 1))
+            x = self._reduce(partial)
+        g(x, L["cross_q"])
         cur.wait_stream(side)
         cv = kv[:, kv.shape[1] // 2:]
-        x = self._reduce(g(self._row_input(cv, L["cross_o"]), L["cross_o"].weight))
-        h = g(x, L["ffn_up"].weight)
-        x = self._reduce(g(self._row_input(h, L["ffn_down"]), L["ffn_down"].weight))
+        x = self._row(cv, L["cross_o"])
+        h = g(x, L["ffn_up"])
+        x = self._row(h, L["ffn_down"])
         return x
 
     def block_forward(self, blk: int, x: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
@@ -420,28 +520,28 @@ class LayerSet:
         if self.concurrent and self.fuse_qkv and x.is_cuda:
             return self._block_forward_fused_overlapped(blk, x, ctx)
         L = {l.name: l for l in self.layers[blk]}
-        g = self.gemm
+        g = self._g
         # self attention: q, k, v column-parallel; the v shard stands in for the attention output
         if self.fuse_qkv:
-            qkv = g(x, L["self_qkv"].weight)
+            qkv = g(x, L["self_qkv"])
             v = qkv[:, 2 * (qkv.shape[1] // 3):]
         else:
-            g(x, L["self_q"].weight)
-            g(x, L["self_k"].weight)
-            v = g(x, L["self_v"].weight)
-        x = self._reduce(g(self._row_input(v, L["self_o"]), L["self_o"].weight))
+            g(x, L["self_q"])
+            g(x, L["self_k"])
+            v = g(x, L["self_v"])
+        x = self._row(v, L["self_o"])
         # cross attention: q on x, k and v on the context
-        g(x, L["cross_q"].weight)
+        g(x, L["cross_q"])
         if self.fuse_qkv:
-            kv = g(ctx, L["cross_kv"].weight)
+            kv = g(ctx, L["cross_kv"])
             cv = kv[:, kv.shape[1] // 2:]
         else:
-            g(ctx, L["cross_k"].weight)
-            cv = g(ctx, L["cross_v"].weight)
-        x = self._reduce(g(self._row_input(cv, L["cross_o"]), L["cross_o"].weight))
+            g(ctx, L["cross_k"])
+            cv = g(ctx, L["cross_v"])
+        x = self._row(cv, L["cross_o"])
         # FFN
-        h = g(x, L["ffn_up"].weight)
-        x = self._reduce(g(self._row_input(h, L["ffn_down"]), L["ffn_down"].weight))
+        h = g(x, L["ffn_up"])
+        x = self._row(h, L["ffn_down"])
         return x
 
     def _row_input(self, col_out: torch.Tensor, row_layer: ShardedLinear) -> torch.Tensor:

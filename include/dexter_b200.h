@@ -63,6 +63,66 @@ int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const
                 int group_size, void* workspace, size_t workspace_bytes, int max_ctas,
                 void* cuda_stream);
 
+/*
+ * dxb_wq_gemm with options.  Replaces the same reference slot; each option stands for a
+ * step the reference takes next to that slot:
+ *   weight_layout  DXB_LAYOUT_DEXTER: `qweight` is the reference quantiser's tensor.
+ *                  DXB_LAYOUT_B200 (int4 only): `qweight` is the output of dxb_relayout_w4,
+ *                  the load-time repack the reference names as its own next step
+ *                  ("pack into int32 words", README.md:147-150 of the reference).
+ *   epilogue       DXB_EPILOGUE_GELU_TANH: tanh-GELU on the bf16 result (after the bias), what
+ *                  the reference applies between the packed FFN linears
+ *                  (python/dexter/models/dreamzero/model.py:279-285; oracle
+ *                  python/dexter/ops/reference/gemm.py:92-100).
+ *   max_ctas       as in dxb_wq_gemm.
+ *   peer_*         peer_world > 1: this GEMM is one rank's K-shard of a row-parallel linear and
+ *                  the sum over the ranks of one NVLink domain is part of the launch (the
+ *                  reference has no tensor parallelism; this replaces a collective after the
+ *                  call).  peer_regions[r] = rank r's region AS MAPPED IN THIS PROCESS (host array
+ *                  of peer_world device pointers), each dxb_fused_reduce_bytes(world,
+ *                  peer_capacity_elems) bytes of peer-mapped memory, zero-filled on every rank
+ *                  before anyone's first call and used for nothing else.  Every rank must make
+ *                  the same sequence of calls with the same M and N (K may differ), each on its
+ *                  own GPU, one call in flight per region; M <= 128, M * N <= peer_capacity_elems,
+ *                  a shape the tensor-core kernel takes (else DXB_ERR_UNSUPPORTED).  Every rank
+ *                  passes the full `bias` (it is added after the sum) and receives the full
+ *                  result in `out`: partial sums travel as bf16 and are added in fp32 in rank
+ *                  order, so all ranks hold identical bits.  Waits for peers are bounded
+ *                  (dxb_set_wait_limit_ms); on expiry DXB_ERR_KERNEL_TIMEOUT is left in the
+ *                  workspace status word.  Plain peer stores and system-scope fences only.
+ * `opts` may be NULL (all defaults).
+ */
+enum { DXB_LAYOUT_DEXTER = 0, DXB_LAYOUT_B200 = 1 };
+enum { DXB_EPILOGUE_NONE = 0, DXB_EPILOGUE_GELU_TANH = 1 };
+typedef struct dxb_gemm_opts {
+  int weight_layout;
+  int epilogue;
+  int max_ctas;
+  int peer_world;
+  int peer_rank;
+  void* const* peer_regions;
+  int64_t peer_capacity_elems;
+} dxb_gemm_opts;
+
+int dxb_wq_gemm_ex(int bits, const void* x, int64_t ldx, const void* qweight, const void* scales,
+                   const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
+                   int group_size, void* workspace, size_t workspace_bytes,
+                   const dxb_gemm_opts* opts, void* cuda_stream);
+
+/* Bytes of one rank's region for the fused sum over ranks (0 for an unsupported world size). */
+size_t dxb_fused_reduce_bytes(int world, int64_t capacity_elems);
+
+/*
+ * Load-time repack of an int4 `qweight` [K/2, N] (python/dexter/quant.py:62-72 layout) into
+ * the layout DXB_LAYOUT_B200 names, or back (`inverse` != 0).  Same shape and size; `out`
+ * may equal `qweight`.  Inside every aligned block of 2 packed rows x 4 byte columns the 16
+ * nibbles are regrouped so that one 32-bit word holds, for 4 columns, the two values of
+ * consecutive k that the tensor-core operand pairs up; nothing moves between blocks, so
+ * column slices (multiples of 4 columns) and row slices (multiples of 2 packed rows) of the
+ * repacked tensor are the repacked slices.  K % 4 == 0 and N % 4 == 0 are required.
+ */
+int dxb_relayout_w4(const void* qweight, void* out, int K, int N, int inverse, void* cuda_stream);
+
 /* The registered kernels gemm/w4a16 and gemm/w8a16
  * (python/dexter/ops/gfx1151/gemm/quantized.py:252-263). */
 int dxb_w4a16(const void* x, int64_t ldx, const void* qweight, const void* scales,
@@ -90,68 +150,16 @@ int dxb_w8a16(const void* x, int64_t ldx, const void* qweight, const void* scale
  *     14B backbones at up to 128 tokens per launch fit);
  *   - the first call on each device looks up the array's device address; make that
  *     first call outside any stream capture;
- *   - all calls share the one array: the counters and the status word are cleared
- *     (cudaMemsetAsync on `cuda_stream`) at the start of every call, partial sums
- *     are overwritten before use; two calls that may run on the GPU at the same
- *     time (different streams, no ordering) race on it and must not be made.
+ *   - all calls share the one array: the tile counters are cleared (cudaMemsetAsync on
+ *     `cuda_stream`) at the start of every call, partial sums are overwritten before
+ *     use; two calls that may run on the GPU at the same time (different streams, no
+ *     ordering) race on it and must not be made;
+ *   - a kernel that gave up on a bounded wait leaves DXB_ERR_KERNEL_TIMEOUT in the array's
+ *     status word, which stays there until dxb_read_status(NULL, stream) has returned it.
  */
 int dxb_wq_gemm_static(int bits, const void* x, int64_t ldx, const void* qweight,
                        const void* scales, const void* zeros, const void* bias, void* out,
                        int64_t ldo, int M, int N, int K, int group_size, void* cuda_stream);
-
-/*
- * Several GEMMs of one layer in ONE launch.  The reference runs a block's linears as
- * successive calls of the kernel slot, one launch each (ops.linear,
- * python/dexter/ops/__init__.py:89-112, called per projection from
- * python/dexter/models/layers.py:44-50); at
- * M <= 128 tokens each of those launches is dominated by its start-up and drain.  A
- * chain hands the whole list to one persistent grid (one CTA per SM): every CTA works
- * through the items in order, the packed-weight pipeline of item i+1 fills while item
- * i drains, and an item whose activations are an earlier item's output waits on a
- * completion count in global memory instead of a kernel boundary.
- *
- * Rules:
- *   - 1 <= n_items <= DXB_CHAIN_MAX; every item must be a shape the tensor-core kernel
- *     takes (dxb_uses_tensor_cores, M <= 128, 16-byte aligned pointers and strides) with
- *     at least 8 units of 128 (int4) or 64 (int8) rows of K; all items share `bits` and
- *     either all or none have zero points; otherwise DXB_ERR_UNSUPPORTED and nothing is
- *     launched (call dxb_wq_gemm per item instead).
- *   - depends_on = index of the EARLIER item whose `out` buffer this item's `x` reads,
- *     or -1 when `x` is ready before the call.  An item may depend on one item only.
- *     Items are started in list order; placing an independent item between a producer
- *     and its consumer hides the hand-over completely.
- *   - no `out` buffer may overlap another item's `out` or any item's `x` other than
- *     that of the items that name it in depends_on.
- *   - `workspace`: at least dxb_chain_workspace_bytes() (a status word and completion
- *     counts; partial sums stay in shared memory), 256-byte aligned, zero-filled once
- *     before its first use; the kernel leaves it clean after every normal completion.
- *     Calls that may overlap on the GPU need different workspaces.
- *   - the grid (clusters of 2, 4 or 8 CTAs, as many as are resident at once) is sized for
- *     a GPU that this stream has to itself while the chain runs.  Every in-kernel wait is
- *     bounded: if part of the grid cannot become resident because other work holds SMs,
- *     the call ends with DXB_ERR_KERNEL_TIMEOUT in dxb_read_status(workspace), it does
- *     not hang.
- * Each item computes what dxb_wq_gemm computes for it (same dequantisation, fp32
- * accumulation, bf16 rounding, bias order); only the split of the K range differs, and the
- * partial sums of a tile are always added in the same order, so runs are reproducible.
- */
-#define DXB_CHAIN_MAX 32
-typedef struct dxb_chain_item {
-  const void* x;
-  int64_t ldx;
-  const void* qweight;
-  const void* scales;
-  const void* zeros;
-  const void* bias;
-  void* out;
-  int64_t ldo;
-  int M, N, K, group_size;
-  int depends_on;
-} dxb_chain_item;
-
-size_t dxb_chain_workspace_bytes(int bits, const dxb_chain_item* items, int n_items, int max_ctas);
-int dxb_wq_gemm_chain(int bits, const dxb_chain_item* items, int n_items, void* workspace,
-                      size_t workspace_bytes, int max_ctas, void* cuda_stream);
 
 /*
  * Tensor-parallel glue for the few-token regime: sum of the row-parallel linears' partial
@@ -182,6 +190,10 @@ int dxb_peer_allreduce(const void* partial, void* out, int64_t elems, void* cons
  * also accepts the smaller amount a 128-token (and 96-token) problem asks for and then
  * launches block by block. */
 size_t dxb_workspace_bytes(int M, int N, int K, int bits);
+/* The same for a call that caps the grid (`max_ctas` of dxb_wq_gemm); a cap can change how
+ * tiles are split and with it the scratch needed.  dxb_wq_gemm also accepts the uncapped
+ * amount: it then hands out whole tiles, which need no partial sums. */
+size_t dxb_workspace_bytes_ex(int M, int N, int K, int bits, int max_ctas);
 
 /*
  * Dense [K, N] bf16 weight, computed with the same bit-pattern arithmetic as the
@@ -191,6 +203,9 @@ size_t dxb_workspace_bytes(int M, int N, int K, int bits);
  */
 int dxb_dequantize(const void* qweight, const void* scales, const void* zeros, void* w_out, int N,
                    int K, int group_size, int bits, void* cuda_stream);
+/* The same for a weight in `weight_layout` (DXB_LAYOUT_*). */
+int dxb_dequantize_ex(const void* qweight, const void* scales, const void* zeros, void* w_out, int N,
+                      int K, int group_size, int bits, int weight_layout, void* cuda_stream);
 
 /* 1 when dxb_wq_gemm runs this shape on the tcgen05 kernel, 0 when it takes the
  * plain CUDA-core kernel (the counterpart of the reference's `accepts` shape
@@ -198,8 +213,14 @@ int dxb_dequantize(const void* qweight, const void* scales, const void* zeros, v
 int dxb_uses_tensor_cores(int M, int N, int K, int group_size, int bits);
 
 /* Synchronises `cuda_stream` and returns the status word of `workspace`:
- * DXB_OK, or DXB_ERR_KERNEL_TIMEOUT if a kernel gave up on a wait. */
+ * DXB_OK, or DXB_ERR_KERNEL_TIMEOUT if a kernel gave up on a wait.  `workspace` == NULL reads
+ * the status word of the scratch built into the library (dxb_wq_gemm_static) and clears it. */
 int dxb_read_status(void* workspace, void* cuda_stream);
+
+/* Upper bound, in milliseconds, of a kernel's wait for another GPU (dxb_peer_allreduce and the
+ * fused sum over ranks of dxb_wq_gemm_ex); process-wide, applies to later calls, about 1000 by
+ * default.  No counterpart in the reference (which has no multi-GPU path). */
+void dxb_set_wait_limit_ms(int ms);
 
 /* Static, NUL-terminated description of a DXB_* code. */
 const char* dxb_strerror(int code);

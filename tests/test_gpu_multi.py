@@ -1,4 +1,6 @@
-"""Tensor-parallel layer set over NCCL on 2 GPUs (skipped with fewer).  -m gpu."""
+"""Tensor-parallel layer set on 2, 4 and 8 GPUs (each skipped where fewer are visible): NCCL
+collectives, the peer all-reduce kernel and the sum fused into the row-parallel GEMMs, every
+rank's output against the unsharded result.  -m gpu."""
 import os
 import socket
 
@@ -62,13 +64,45 @@ def _worker(rank, world, port, results):
         y5 = fused.forward(x, ctx)
         torch.cuda.synchronize()
         results[rank + 3 * world] = y5.float().cpu().numpy()
+        # reduce-scatter + all-gather instead of the all-reduce
+        rsag = tp.LayerSet.build("5b", blocks=1, rank=rank, world=world, seed=3, device=f"cuda:{rank}",
+                                 collective="rs_ag")
+        y6 = rsag.forward(x, ctx)
+        torch.cuda.synchronize()
+        results[rank + 4 * world] = y6.float().cpu().numpy()
+        # the sum over ranks inside the row-parallel GEMM's own launch: plain and overlapped
+        # schedules, eagerly and as a replayed CUDA graph
+        if fused.enable_fused_reduce(83, f"cuda:{rank}"):
+            y7 = fused.forward(x, ctx)
+            torch.cuda.synchronize()
+            results[rank + 5 * world] = y7.float().cpu().numpy()
+            fused.concurrent = False
+            y8 = fused.forward(x, ctx)
+            torch.cuda.synchronize()
+            fused.concurrent = True
+            assert torch.equal(y7, y8)  # same launches, same arithmetic, another schedule
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                y9 = fused.forward(x, ctx)
+            for _ in range(3):
+                y9.zero_()
+                graph.replay()
+                torch.cuda.synchronize()
+                assert torch.equal(y9, y7)
+            from dexter_labs_b200 import ops
+
+            assert ops.last_status() == 0
+            results["fused"] = True
+        else:
+            results["fused_error"] = getattr(fused, "_peer_error", "unknown")
     finally:
         dist.destroy_process_group()
 
 
-def test_two_gpu_layer_set_matches_one_gpu(b200_lib):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_layer_set_matches_one_gpu(b200_lib, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     from dexter_labs_b200 import tp
 
     single = tp.LayerSet.build("5b", blocks=1, seed=3)
@@ -76,12 +110,17 @@ def test_two_gpu_layer_set_matches_one_gpu(b200_lib):
     x = torch.randn(83, 3072).to(torch.bfloat16).cuda()
     ctx = torch.randn(83, 3072).to(torch.bfloat16).cuda()
     want = single.forward(x, ctx).float().cpu().numpy()
-    world = 2
     results = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
     assert results.get("peer"), f"peer all-reduce could not be set up: {results.get('peer_error')}"
-    for rank in range(4 * world):
-        e = np.abs(results[rank] - want).max() / max(np.abs(want).max(), 1e-6)
-        assert e < 1e-2, (rank, e)
-    # every rank holds the same bits after the peer all-reduce (fixed summation order)
-    assert np.array_equal(results[2 * world], results[2 * world + 1])
+    assert results.get("fused"), f"fused sum could not be set up: {results.get('fused_error')}"
+    # NCCL all-reduce (plain, overlapped), peer kernel, fused q/k/v, rs+ag, fused sum: every
+    # rank's output against the unsharded result
+    for slot in range(6 * world):
+        e = np.abs(results[slot] - want).max() / max(np.abs(want).max(), 1e-6)
+        assert e < 1e-2, (slot // world, slot % world, e)
+    # every rank holds the same bits after the peer all-reduce and after the fused sum (fixed
+    # summation order)
+    for base in (2 * world, 5 * world):
+        for rank in range(1, world):
+            assert np.array_equal(results[base], results[base + rank]), (base // world, rank)

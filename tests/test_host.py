@@ -216,23 +216,33 @@ def test_strerror_and_argument_checks(b200_lib):
     assert b200_lib.dxb_uses_tensor_cores(83, 3072, 192, 64, 8) == 0      # int8 with K % 128 != 0
 
 
-def test_chain_and_peer_entry_points_check_their_arguments(b200_lib):
-    """Argument checks of the list and all-reduce entry points return before any launch."""
+def test_peer_and_option_entry_points_check_their_arguments(b200_lib):
+    """Argument checks of the all-reduce, re-layout and option entry points return before any launch."""
     from dexter_labs_b200 import _lib
 
-    assert ctypes.sizeof(_lib.ChainItem) == 88  # 8 pointers/strides of 8 bytes + 5 ints, padded
-    items = (_lib.ChainItem * 1)()
-    assert b200_lib.dxb_wq_gemm_chain(3, items, 1, None, 0, 0, None) == -1     # bits
-    assert b200_lib.dxb_wq_gemm_chain(4, None, 1, None, 0, 0, None) == -2      # no items
-    assert b200_lib.dxb_wq_gemm_chain(4, items, 0, None, 0, 0, None) == -4     # empty list
-    assert b200_lib.dxb_wq_gemm_chain(4, items, _lib.DXB_CHAIN_MAX + 1, None, 0, 0, None) == -4
-    assert b200_lib.dxb_chain_workspace_bytes(4, items, 0, 0) == 0
+    vp = ctypes.c_void_p
+    assert ctypes.sizeof(_lib.GemmOpts) == 40  # 5 ints, padding, a pointer, an int64
+    assert b200_lib.dxb_relayout_w4(None, vp(16), 256, 64, 0, None) == -2
+    assert b200_lib.dxb_relayout_w4(vp(16), vp(16), 254, 64, 0, None) == -3   # whole row pairs
+    assert b200_lib.dxb_relayout_w4(vp(16), vp(16), 256, 62, 0, None) == -3   # whole 32-bit words
+    assert b200_lib.dxb_fused_reduce_bytes(9, 1024) == 0 and b200_lib.dxb_fused_reduce_bytes(2, 0) == 0
+    assert b200_lib.dxb_fused_reduce_bytes(8, 1024) > b200_lib.dxb_fused_reduce_bytes(2, 1024) > 2 * 2 * 1024 * 2
+    bad = _lib.GemmOpts(7, 0, 0, 0, 0, None, 0)  # unknown layout
+    assert b200_lib.dxb_wq_gemm_ex(4, vp(16), 3072, vp(16), vp(16), None, None, vp(16), 3072, 83, 3072, 3072,
+                                   128, None, 0, ctypes.byref(bad), None) == -4
+    bad = _lib.GemmOpts(0, 9, 0, 0, 0, None, 0)  # unknown epilogue
+    assert b200_lib.dxb_wq_gemm_ex(4, vp(16), 3072, vp(16), vp(16), None, None, vp(16), 3072, 83, 3072, 3072,
+                                   128, None, 0, ctypes.byref(bad), None) == -4
+    bad = _lib.GemmOpts(0, 0, 0, 9, 0, None, 0)  # more ranks than one NVLink domain holds
+    assert b200_lib.dxb_wq_gemm_ex(4, vp(16), 3072, vp(16), vp(16), None, None, vp(16), 3072, 83, 3072, 3072,
+                                   128, None, 0, ctypes.byref(bad), None) == -3
+    assert b200_lib.dxb_dequantize_ex(vp(16), vp(16), None, vp(16), 16, 256, 128, 8, 1, None) == -4
+    assert b200_lib.dxb_workspace_bytes_ex(83, 3072, 3072, 4, 0) == b200_lib.dxb_workspace_bytes(83, 3072, 3072, 4)
     # peer all-reduce: region size is plain arithmetic; bad ranks and sizes are refused
     one = b200_lib.dxb_peer_allreduce_bytes(2, 1024)
     assert one > 2 * 2 * 1024 * 2 and b200_lib.dxb_peer_allreduce_bytes(8, 1024) > one
     assert b200_lib.dxb_peer_allreduce_bytes(9, 1024) == 0
     assert b200_lib.dxb_peer_allreduce_bytes(2, 0) == 0
-    vp = ctypes.c_void_p
     regions = (vp * 2)(vp(256), vp(512))
     assert b200_lib.dxb_peer_allreduce(None, vp(16), 8, regions, 8, 0, 2, None, None) == -2
     assert b200_lib.dxb_peer_allreduce(vp(16), vp(16), 8, regions, 8, 2, 2, None, None) == -3   # rank
