@@ -6,6 +6,7 @@ reference project is importable, in ``dexter.registry`` as well.
 """
 from . import platform, quant, registry  # noqa: F401
 from . import ops  # noqa: F401  (loads libdexter_b200.so, registers the kernels)
+from . import custom_op  # noqa: F401  (declares torch.ops.dexter_b200.wq_gemm)
 from .ops import KERNEL_NAMES, dequantize, linear, w4a16, w8a16  # noqa: F401
 from .quant import QuantizedWeight, quantize  # noqa: F401
 

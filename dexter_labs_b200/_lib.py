@@ -9,7 +9,11 @@ import ctypes
 from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libdexter_b200.so"
+import os
+
+# the in-tree build, unless DEXTER_B200_LIBRARY names another build of the same library
+# (e.g. one compiled with -DDXB_TRACE for in-kernel time stamps)
+LIB_PATH = Path(os.environ.get("DEXTER_B200_LIBRARY") or Path(__file__).resolve().parent / "libdexter_b200.so")
 
 OK = 0
 ERRORS = {
@@ -26,7 +30,8 @@ class GemmOpts(ctypes.Structure):
     """``dxb_gemm_opts`` of include/dexter_b200.h."""
     _fields_ = [("weight_layout", c_int), ("epilogue", c_int), ("max_ctas", c_int),
                 ("peer_world", c_int), ("peer_rank", c_int),
-                ("peer_regions", ctypes.POINTER(c_void_p)), ("peer_capacity_elems", c_int64)]
+                ("peer_regions", ctypes.POINTER(c_void_p)), ("peer_capacity_elems", c_int64),
+                ("serialize", c_int)]
 
 
 # name -> (restype, argtypes); one entry per symbol declared in include/dexter_b200.h

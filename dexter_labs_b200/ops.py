@@ -79,15 +79,20 @@ def _run(bits: int, x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor
     if k_in != k_dim:
         raise ValueError(f"x has K={k_in} but the packed weight has K={k_dim}")
     n = qweight.shape[1]
+    # A weight tensor that has to be copied here is written by the kernel right before the
+    # GEMM on this stream, which the GEMM must then not overtake (it normally starts early
+    # and reads its weights at once): such a call is launched in plain stream order.
+    copied = False
     if not qweight.is_contiguous():
         if layout != "dexter":
             raise ValueError("a re-laid-out weight must be contiguous")
-        qweight = qweight.contiguous()
-    scales = scales if scales.is_contiguous() else scales.contiguous()
+        qweight, copied = qweight.contiguous(), True
+    if not scales.is_contiguous():
+        scales, copied = scales.contiguous(), True
     if zeros is not None and not zeros.is_contiguous():
-        zeros = zeros.contiguous()
+        zeros, copied = zeros.contiguous(), True
     if bias is not None and not bias.is_contiguous():
-        bias = bias.contiguous()
+        bias, copied = bias.contiguous(), True
 
     x2 = x.reshape(-1, k_in)
     if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
@@ -104,16 +109,18 @@ def _run(bits: int, x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor
                         epilogue=epilogue, reduce=reduce)
     if layout == "dexter" and bits == 4:
         # load-time repack, cached per weight tensor (see prepared_w4)
-        relaid = prepared_w4(qweight, m, n, k_dim, group_size)
+        relaid = None if copied else prepared_w4(qweight, m, n, k_dim, group_size)
         if relaid is not None:
-            qweight, layout = relaid, "b200"
+            # a copy made just now was written by the kernel right before this GEMM
+            copied = relaid[1]
+            qweight, layout = relaid[0], "b200"
     stream = _raw_stream(dev)
     key = (m, n, k_dim, bits, max_ctas)
     need = _need_cache.get(key)
     if need is None:
         need = _need_cache[key] = _LIB.dxb_workspace_bytes_ex(m, n, k_dim, bits, max_ctas)
     ws = _workspace(x.device, stream, need)
-    opts = _lib.GemmOpts(_LAYOUTS[layout], _EPILOGUES[epilogue], max_ctas, 0, 0, None, 0)
+    opts = _lib.GemmOpts(_LAYOUTS[layout], _EPILOGUES[epilogue], max_ctas, 0, 0, None, 0, 1 if copied else 0)
     if reduce is not None:
         opts.peer_world, opts.peer_rank = reduce.world, reduce.rank
         opts.peer_regions, opts.peer_capacity_elems = reduce._ptrs, reduce.capacity
@@ -166,18 +173,19 @@ def relayout_w4(qweight: torch.Tensor, *, inverse: bool = False,
     return dst
 
 
-def prepared_w4(qweight: torch.Tensor, m: int, n: int, k_dim: int, group_size: int) -> Optional[torch.Tensor]:
+def prepared_w4(qweight: torch.Tensor, m: int, n: int, k_dim: int,
+                group_size: int) -> Optional[Tuple[torch.Tensor, bool]]:
     """The cached repacked copy of ``qweight`` for calls that come in with the reference
-    layout (the registered kernels), or None where the repack does not apply: shapes the
-    plain CUDA-core kernel serves, a stream that is being captured before the copy exists,
-    ``DEXTER_B200_RELAYOUT=0``.  The copy is made on the first call with a given tensor
-    object and dropped when that tensor is freed or modified in place."""
+    layout (the registered kernels), as ``(copy, made_just_now)``, or None where the repack
+    does not apply: shapes the plain CUDA-core kernel serves, a stream that is being captured
+    before the copy exists, ``DEXTER_B200_RELAYOUT=0``.  The copy is made on the first call
+    with a given tensor object and dropped when that tensor is freed or modified in place."""
     if not _AUTO_RELAYOUT:
         return None
     key = id(qweight)
     hit = _relaid.get(key)
     if hit is not None and hit[0]() is qweight and hit[1] == qweight._version:
-        return hit[2]
+        return hit[2], False
     if (qweight.shape[0] % 2 or n % 4 or qweight.data_ptr() % 16
             or not _LIB.dxb_uses_tensor_cores(m, n, k_dim, group_size, 4)
             or torch.cuda.is_current_stream_capturing()):
@@ -185,7 +193,7 @@ def prepared_w4(qweight: torch.Tensor, m: int, n: int, k_dim: int, group_size: i
     relaid = relayout_w4(qweight)
     _relaid[key] = (weakref.ref(qweight, lambda _r, key=key: _relaid.pop(key, None)),
                     qweight._version, relaid)
-    return relaid
+    return relaid, True
 
 
 def last_status(device: Optional[torch.device] = None) -> int:
@@ -224,13 +232,21 @@ def w4a16(x, qweight, scales, zeros, bias, group_size, *, max_ctas: int = 0, lay
     ``reduce`` (a :class:`FusedReduce`) makes the call one rank's K-shard of a
     row-parallel linear and returns the sum over ranks.
     """
+    if _plain_call(max_ctas, layout, epilogue, reduce) and torch.compiler.is_compiling():
+        return torch.ops.dexter_b200.wq_gemm(x, qweight, scales, zeros, bias, group_size, 4)
     return _run(4, x, qweight, scales, zeros, bias, group_size, max_ctas, layout=layout,
                 epilogue=epilogue, reduce=reduce)
+
+
+def _plain_call(max_ctas, layout, epilogue, reduce) -> bool:
+    return max_ctas == 0 and layout == "dexter" and epilogue is None and reduce is None
 
 
 def w8a16(x, qweight, scales, zeros, bias, group_size, *, max_ctas: int = 0,
           epilogue: Optional[str] = None, reduce: Optional["FusedReduce"] = None):
     """int8 weight-only GEMM, bf16 in / bf16 out (keywords: see :func:`w4a16`)."""
+    if _plain_call(max_ctas, "dexter", epilogue, reduce) and torch.compiler.is_compiling():
+        return torch.ops.dexter_b200.wq_gemm(x, qweight, scales, zeros, bias, group_size, 8)
     return _run(8, x, qweight, scales, zeros, bias, group_size, max_ctas, epilogue=epilogue,
                 reduce=reduce)
 

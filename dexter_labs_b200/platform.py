@@ -5,6 +5,11 @@ that the quantised-GEMM path touches (``Capability`` :169-185, ``PlatformInfo``
 :129-166, NVIDIA / CPU detection :224-264, ``current_platform`` /
 ``override_platform`` :267-278), so the backend registers and is selected the
 same way with or without the reference installed.
+
+A stand-in: it is used only where the reference project is not importable (a machine that has
+this package alone).  Where the reference is present its own module is the one in charge --
+``ops.register_with`` plugs the kernels into it -- and the tests drive that one
+(``tests/test_reference_api.py``).
 """
 from __future__ import annotations
 

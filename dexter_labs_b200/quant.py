@@ -15,6 +15,11 @@ Layout (``quant.py:34-72`` in the reference):
 * ``scales`` / ``zeros`` are ``[K // group_size, N]`` in the weight's dtype;
   ``zeros`` is ``None`` for the symmetric grid; 4-bit zero points carry
   ``+128`` (``BF16_MAGIC_BIAS``).
+
+A stand-in: it is used only where the reference project is not importable (a machine that has
+this package alone).  Where the reference is present its own module is the one in charge --
+``ops.register_with`` plugs the kernels into it -- and the tests drive that one
+(``tests/test_reference_api.py``).
 """
 from __future__ import annotations
 

@@ -10,6 +10,11 @@ the same names and rules:
 * ``accepts(*shape_args)`` lets a kernel decline a call (it is also called with
   no arguments by benchmarks, and must then answer for the general case);
 * ``DEXTER_KERNEL=gemm/w4a16:<name>`` pins one implementation.
+
+A stand-in: it is used only where the reference project is not importable (a machine that has
+this package alone).  Where the reference is present its own module is the one in charge --
+``ops.register_with`` plugs the kernels into it -- and the tests drive that one
+(``tests/test_reference_api.py``).
 """
 from __future__ import annotations
 

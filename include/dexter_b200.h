@@ -57,6 +57,13 @@ enum {
  * that several independent GEMMs can run side by side on different streams.
  * Any M: up to 128 tokens are one accumulator block; more tokens are processed as blocks of
  * 128 inside ONE launch (every (token block, 128-column tile) pair is a tile of the grid).
+ * Launch order: the kernel is launched with programmatic stream serialisation, so it may
+ * begin while the kernel before it on `cuda_stream` is still running.  It waits for that
+ * kernel before it reads `x` or writes `out` / `workspace`, but it reads `qweight`, `scales`,
+ * `zeros` and `bias` at once: these must be complete when the call is enqueued, i.e. they must
+ * not be produced by the immediately preceding kernel of the same stream (weights are; a
+ * caller that slices or copies weights per call must not).  DEXTER_B200_PDL=0 turns the
+ * early start off.
  */
 int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const void* scales,
                 const void* zeros, const void* bias, void* out, int64_t ldo, int M, int N, int K,
@@ -90,6 +97,9 @@ int dxb_wq_gemm(int bits, const void* x, int64_t ldx, const void* qweight, const
  *                  order, so all ranks hold identical bits.  Waits for peers are bounded
  *                  (dxb_set_wait_limit_ms); on expiry DXB_ERR_KERNEL_TIMEOUT is left in the
  *                  workspace status word.  Plain peer stores and system-scope fences only.
+ *   serialize      nonzero: plain stream order for this launch (no early start, see dxb_wq_gemm);
+ *                  for a caller whose `qweight` / `scales` / `zeros` / `bias` were just written by
+ *                  the preceding kernel of the stream.
  * `opts` may be NULL (all defaults).
  */
 enum { DXB_LAYOUT_DEXTER = 0, DXB_LAYOUT_B200 = 1 };
@@ -102,6 +112,7 @@ typedef struct dxb_gemm_opts {
   int peer_rank;
   void* const* peer_regions;
   int64_t peer_capacity_elems;
+  int serialize;
 } dxb_gemm_opts;
 
 int dxb_wq_gemm_ex(int bits, const void* x, int64_t ldx, const void* qweight, const void* scales,

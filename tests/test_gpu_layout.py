@@ -179,7 +179,7 @@ def test_capped_grids_run_in_the_uncapped_workspace(d, b200_lib, m, k, n):
         assert b200_lib.dxb_workspace_bytes_ex(m, n, k, 4, cap) >= 256
         if want is None:
             want = got
-        assert err(got.float(), want.float()) < 2e-3, cap  # only the K-split order differs
+        assert err(got.float(), want.float()) < TOL, cap  # only the K-split order differs (a bf16 ulp)
 
 
 # ----------------------------------------------- a bounded wait that runs out
@@ -246,7 +246,7 @@ def test_fused_sum_wait_runs_out_without_hanging(d, b200_lib):
                               _ptr(out), n, m, n, k, 128, _ptr(ws), need, 0, stream)
     assert rc == 0 and b200_lib.dxb_read_status(_ptr(ws), stream) == 0
     want = d.ops.w4a16(x, qw.qweight, qw.scales, None, bias, 128)
-    assert err(out.float(), want.float()) < 2e-3
+    assert err(out.float(), want.float()) < 5e-3
 
 
 def test_fused_sum_with_one_rank_equals_the_plain_call(d, b200_lib):
@@ -286,3 +286,19 @@ def test_fused_sum_with_one_rank_equals_the_plain_call(d, b200_lib):
     rc = b200_lib.dxb_wq_gemm_ex(8, _ptr(x), k, _ptr(qw.qweight), _ptr(qw.scales), None, None,
                                  _ptr(out), n, m, n, k // 2, 128, _ptr(ws), need, ctypes.byref(opts), stream)
     assert rc == -4
+
+
+# ------------------------------------------------------------ dispatcher-level op
+def test_custom_op_matches_the_direct_call_and_traces(d):
+    x, qw, bias = _problem(d, 83, 1024, 512, 4, 128, False, seed=9)
+    direct = d.ops.w4a16(x, qw.qweight, qw.scales, qw.zeros, bias, 128)
+    via_op = torch.ops.dexter_b200.wq_gemm(x, qw.qweight, qw.scales, qw.zeros, bias, 128, 4)
+    assert torch.equal(direct, via_op)
+    torch.library.opcheck(torch.ops.dexter_b200.wq_gemm.default, (x, qw.qweight, qw.scales, qw.zeros, bias, 128, 4),
+                          test_utils=("test_schema", "test_faketensor"))
+
+    def fn(inp):
+        return d.ops.w4a16(inp * 2, qw.qweight, qw.scales, qw.zeros, bias, 128) + 1
+
+    compiled = torch.compile(fn, backend="eager", fullgraph=True)  # the op must trace as one node
+    assert torch.equal(compiled(x), fn(x))

@@ -221,7 +221,7 @@ def test_peer_and_option_entry_points_check_their_arguments(b200_lib):
     from dexter_labs_b200 import _lib
 
     vp = ctypes.c_void_p
-    assert ctypes.sizeof(_lib.GemmOpts) == 40  # 5 ints, padding, a pointer, an int64
+    assert ctypes.sizeof(_lib.GemmOpts) == 48  # 5 ints, padding, a pointer, an int64, an int, padding
     assert b200_lib.dxb_relayout_w4(None, vp(16), 256, 64, 0, None) == -2
     assert b200_lib.dxb_relayout_w4(vp(16), vp(16), 254, 64, 0, None) == -3   # whole row pairs
     assert b200_lib.dxb_relayout_w4(vp(16), vp(16), 256, 62, 0, None) == -3   # whole 32-bit words
@@ -248,3 +248,22 @@ def test_peer_and_option_entry_points_check_their_arguments(b200_lib):
     assert b200_lib.dxb_peer_allreduce(vp(16), vp(16), 8, regions, 8, 2, 2, None, None) == -3   # rank
     assert b200_lib.dxb_peer_allreduce(vp(16), vp(16), 12, regions, 16, 0, 2, None, None) == -3  # % 8
     assert b200_lib.dxb_peer_allreduce(vp(16), vp(16), 16, regions, 8, 0, 2, None, None) == -3   # capacity
+
+
+def test_custom_op_is_declared_with_a_shape_function(b200_lib):
+    """torch.ops.dexter_b200.wq_gemm traces without a GPU: output shape, dtype and device come
+    from the shape-only implementation; a K mismatch is refused while tracing."""
+    import dexter_labs_b200  # noqa: F401
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():
+        x = torch.empty(2, 83, 3072, dtype=torch.bfloat16, device="cuda")
+        q4 = torch.empty(1536, 14336, dtype=torch.uint8, device="cuda")
+        q8 = torch.empty(3072, 512, dtype=torch.uint8, device="cuda")
+        s = torch.empty(24, 14336, dtype=torch.bfloat16, device="cuda")
+        y = torch.ops.dexter_b200.wq_gemm(x, q4, s, None, None, 128, 4)
+        assert y.shape == (2, 83, 14336) and y.dtype == torch.bfloat16 and y.device.type == "cuda"
+        y = torch.ops.dexter_b200.wq_gemm(x, q8, s[:, :512], None, None, 128, 8)
+        assert y.shape == (2, 83, 512)
+        with pytest.raises(Exception):
+            torch.ops.dexter_b200.wq_gemm(x, q8, s, None, None, 128, 4)  # K = 6144 != 3072
