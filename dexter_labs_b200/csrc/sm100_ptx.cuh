@@ -42,22 +42,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-#ifdef DXB_SPIN_WAITS
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
       "selp.u32 %0, 1, 0, p;\n\t}\n"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }
-// Same test with an explicit suspend-time hint: the hardware may park the thread for up to
-// `hint_ns` until the phase completes.  Measured on B200: a thread parked with a long hint is
-// woken late (about 0.6 us after the phase completed), which put ~750 cycles of pure
-// hand-over latency on every unit of the pipeline; the hot waits therefore use the plain
-// form above in a loop (its own, short, system-defined suspend window wakes promptly).
+// Same test, but the hardware may park the thread for up to `hint_ns` until the
+// phase completes, instead of returning at once: a waiting warp then costs no
+// issue slots and is woken by the barrier itself.  (Loops of the plain form and of
+// mbarrier.test_wait were measured as well: the same or slightly slower.)
 __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity,
                                                      uint32_t hint_ns) {
   uint32_t ok;
@@ -71,31 +66,20 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
   return ok != 0;
 }
 
-// Upper bound of one wait, in SM clock cycles (about a second at 2 GHz).
-constexpr long long kWaitCycles = 2000000000ll;
+// Upper bound of one wait: kWaitTries parked attempts of kWaitHintNs each (about
+// one second in all, whatever the clock).
 constexpr uint32_t kWaitHintNs = 1000000u;
 constexpr uint32_t kWaitTries = 1000u;
 
 // Bounded wait on an mbarrier phase.  `abort_flag` is a CTA-shared word: once
 // any role gives up it is set, and every other wait in the CTA returns false
-// at its next check so the whole CTA drains to its tear-down.
+// at its next poll so the whole CTA drains to its tear-down.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-#ifdef DXB_PARKED_WAITS
   for (uint32_t tries = 0; tries < kWaitTries; ++tries) {
     if (mbar_try_wait_parked(bar, parity, kWaitHintNs)) return true;
     if (*abort_flag) return false;
   }
-#else
-  const long long t0 = clock64();
-  for (uint32_t n = 1;; ++n) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((n & 63u) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) break;
-    }
-  }
-#endif
   *abort_flag = 1;
   return false;
 }

@@ -109,11 +109,8 @@ __host__ __device__ inline int owner_of(long long u, long long total, long long 
 // ready[t]: unit slot t has its activations in shared memory (TMA bytes) AND its
 // dequantised weights in TMEM (128 arrivals of one team); free[t]: the MMAs that
 // read slot t are done (one tcgen05.commit), so both may be overwritten.
-// last: the accumulator of the CTA's LAST segment is complete (one tcgen05.commit, one phase
-// only: the dequant warps wait on it long in advance, which the recurring acc_full barriers
-// could not express -- a parity wait aliases when the waiter is two phases ahead).
 constexpr int kBarFullW = 0, kBarEmptyW = 16, kBarReady = 32, kBarFree = 36, kBarAccFull = 40,
-              kBarAccEmpty = 42, kBarLast = 44, kNumBars = 45;
+              kBarAccEmpty = 42, kNumBars = 44;
 
 __device__ __forceinline__ uint32_t bar_count(int i) {
   if (i < kBarEmptyW) return 1;                    // full_w: producer's expect_tx
@@ -122,7 +119,6 @@ __device__ __forceinline__ uint32_t bar_count(int i) {
   if (i < kBarReady) return kTeamWarps;            // empty_w: the four warps of one team
   if (i < kBarFree) return kTeamWarps + 1;         // ready: team warps + activation producer
   if (i < kBarAccEmpty) return 1;                  // free, acc_full: one tcgen05.commit
-  if (i == kBarLast) return 1;                     // last: one tcgen05.commit
   return kEpilogueThreads / 32;                    // acc_empty: the four epilogue warps
 }
 

@@ -171,7 +171,11 @@ struct WqParams {
 // tanh-GELU of a value that has already been rounded to bf16, as the reference applies it
 // between the FFN linears (torch gelu(approximate="tanh") on the bf16 output of the up
 // projection, python/dexter/models/dreamzero/model.py:279-285): evaluated in fp32, rounded once.
+#ifdef DXB_GELU_NOINLINE
+__device__ __noinline__ float gelu_tanh(float v) {
+#else
 __device__ __forceinline__ float gelu_tanh(float v) {
+#endif
   const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
   return 0.5f * v * (1.0f + tanhf(inner));
 }
@@ -215,10 +219,6 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __shared__ int abort_flag;
   __shared__ long long t_start;
 
-  // The next kernel of the stream may be launched as soon as every CTA of this grid is
-  // running: its weight loads and conversion do not depend on this kernel, and it waits
-  // (pdl_wait) before it touches activations or outputs.
-  pdl_launch_dependents();
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t w_ring = smem0;
   const uint32_t x_ring = smem0 + p.w_stages * W_STAGE;
@@ -247,10 +247,9 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const int ku_begin = u_begin - tile_begin * U;
 
   // Packed-weight producers (warps 0 and 3, alternate units): cursor of the next unit to load.
-  // They start BEFORE the CTA-wide set-up barrier: the weights depend on nothing (not on the
-  // previous kernel of the stream either), and the first bytes from HBM are the longest
-  // latency of a short launch.  Each producer initialises the "full" barriers of its own
-  // stages, fences, and fills its half of the ring; the loop after the barrier carries on.
+  // (Issuing the first loads before the CTA-wide set-up barrier, triggering the dependent
+  // launch earlier, and staggering the teams' first conversions were all measured: each
+  // made the launch slightly slower, so the plain order stays.)
   const int wp = warp == 0 ? 0 : 1;
   int w_u = u_begin + wp, w_tile = tile_begin, w_ku = ku_begin + wp, w_s = wp, w_ntile = 0;
   uint32_t w_ph = 0;
@@ -287,9 +286,6 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     __syncwarp();
     while (w_ku >= U) { w_ku -= U; ++w_tile; }
     w_ntile = MULTI ? w_tile % p.tiles_n : 0;
-    // Two stages per producer now (enough bytes in flight to cover the first-byte latency
-    // without holding up the set-up barrier); the rest of the first pass right after it.
-    for (int first = 0; first < 2 && w_u < u_end; ++first) w_issue();
   } else if (warp == 2 && lane == 0) {
     tma_prefetch_desc(&tm_x);
   } else if (warp == 1) {
@@ -300,6 +296,9 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem0 = tmem_base_s;
+  // The next kernel of the stream may start now: its weight loads and conversion do not
+  // depend on this kernel; it waits (pdl_wait) before it touches activations or outputs.
+  pdl_launch_dependents();
 
   volatile int* abortp = &abort_flag;
 
@@ -325,18 +324,30 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     }
   };
   int pending_acc = -1;  // cluster mode with aliased receive buffers: accumulator still to be sent
-  int pending_wk = 0, pending_nwk = 1;
 
   // ------------------------------------------------------------------ epilogue of one segment
-  // A segment = this CTA's units of one tile, summed in accumulator `b`.  Workers are the
-  // epilogue warp of each TMEM lane quadrant and, for the CTA's LAST segment, the four
-  // dequant warps of that quadrant as well (they have nothing left to convert): worker `wk`
-  // of `nwk` takes the 16-column (token) chunks wk, wk + nwk, ...  `wtid` numbers the
-  // `nthr` participating threads.  Accumulator lane 32q + 8b + g holds weight column
-  // 32q + 4g + b (see the dequant mapping), so the 16x128b load shape hands thread (g, c)
-  // the four consecutive columns 4g..4g+3 of token 4*rep + c: one 8-byte store each.
-  // Returns false when a bounded wait ran out.
-  auto epilogue_segment = [&](int tile, int ku0, int nun, int b, int wk, int nwk, int wtid, int nthr) -> bool {
+  // A segment = this CTA's units of one tile, summed in accumulator `b`; run by the four
+  // epilogue warps (one per TMEM lane quadrant).  Accumulator lane 32q + 8b + g holds weight
+  // column 32q + 4g + b (see the dequant mapping), so the 16x128b load shape hands thread
+  // (g, c) the four consecutive columns 4g..4g+3 of token 4*rep + c: one 8-byte store each.
+  // Returns false when a bounded wait ran out.  (Letting the then idle dequant warps share
+  // the last segment's columns was measured: it shortens a whole tile's epilogue by 0.3 us
+  // but its register cost slows the cluster-split launches by more.)
+  // Bias of this thread's four columns of a tile (fetched before waiting for the accumulator,
+  // so that its latency is not added to the tail of the tile).
+  auto load_bias4 = [&](int tile, float (&bias4)[4]) {
+    const int ntile = MULTI ? tile % p.tiles_n : tile;
+    const int n = ntile * kTileN + 32 * (warp & 3) + 4 * (lane >> 2);
+    bias4[0] = bias4[1] = bias4[2] = bias4[3] = 0.f;
+    if (p.bias != nullptr && n < p.N) {
+      const uint2 bb = __ldg(reinterpret_cast<const uint2*>(p.bias + n));
+      bias4[0] = bf16lo_f32(bb.x); bias4[1] = bf16hi_f32(bb.x);
+      bias4[2] = bf16lo_f32(bb.y); bias4[3] = bf16hi_f32(bb.y);
+    }
+  };
+  auto epilogue_segment = [&](int tile, int ku0, int nun, int b, const float (&bias4)[4]) -> bool {
+    constexpr int wk = 0, nwk = 1, nthr = kEpilogueThreads;  // the four epilogue warps, all columns
+    const int wtid = (warp - 4) * 32 + lane;
     const int q = warp & 3;
     const int c = lane & 3;
     const int g = lane >> 2;
@@ -352,16 +363,19 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // Sum over ranks fused into this launch (one token block only): finished rows go to
     // every rank's receive buffer instead of `out`; fused_finish then completes the tile.
     const bool fused = p.peer.world > 1;
+    const bool plain = !fused && p.epilogue == DXB_EPILOGUE_NONE;
     const unsigned parity =
         fused ? (__ldcg(reinterpret_cast<const unsigned*>(p.peer.region[p.peer.rank])) & 1u) : 0u;
     auto fused_finish = [&]() -> bool {
-      __threadfence_system();
-      named_bar_sync(nthr == kEpilogueThreads ? 1 : 2, nthr);
+      // The barrier orders every participant's peer stores before the signalling threads;
+      // their release at system scope is cumulative, so it covers all of them (a system
+      // fence costs about 1.7 us on this machine: one per rank to signal, not one per thread).
+      named_bar_sync(1, nthr);
       if (wtid < p.peer.world) {
         fused_signal(p.peer, ntile, wtid, static_cast<unsigned>(m_rows));
         fused_wait(p.peer, ntile, wtid, static_cast<unsigned>(m_rows), abortp);
       }
-      named_bar_sync(nthr == kEpilogueThreads ? 1 : 2, nthr);
+      named_bar_sync(1, nthr);
       if (*abortp) return false;
       const int c4 = (wtid & 31) * 4;
       const int nn = ntile * kTileN + c4;
@@ -380,13 +394,6 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
       return true;
     };
-    // The bias does not depend on the accumulator: fetched before the data is looked at.
-    float bias4[4] = {0.f, 0.f, 0.f, 0.f};
-    if (ku0 == 0 && has_bias && n_ok) {  // whole tiles and shared tiles this CTA finishes
-      const uint2 bb = __ldg(reinterpret_cast<const uint2*>(p.bias + n));
-      bias4[0] = bf16lo_f32(bb.x); bias4[1] = bf16hi_f32(bb.x);
-      bias4[2] = bf16lo_f32(bb.y); bias4[3] = bf16hi_f32(bb.y);
-    }
     const uint32_t d_tmem = tmem_addr(tmem0 + b * p.NU, 32 * q, 0);
     if (whole) {
       for (int c0 = 16 * wk; c0 < p.NU; c0 += 16 * nwk) {
@@ -398,15 +405,26 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (int rep = 0; rep < 4; ++rep) {
           const int m = c0 + 4 * rep + c;
           if (n_ok && m < m_rows) {
-            if (fused)
-              fused_push4(p.peer, parity, static_cast<long long>(m) * p.N + n,
-                          __uint_as_float(ra[2 * rep]), __uint_as_float(ra[2 * rep + 1]),
-                          __uint_as_float(rb[2 * rep]), __uint_as_float(rb[2 * rep + 1]));
-            else
-              *reinterpret_cast<uint2*>(p.out + static_cast<long long>(row0 + m) * p.ldo + n) =
-                  finish_row4(__uint_as_float(ra[2 * rep]), __uint_as_float(ra[2 * rep + 1]),
-                              __uint_as_float(rb[2 * rep]), __uint_as_float(rb[2 * rep + 1]),
-                              bias4, has_bias, p.epilogue);
+            const float f0 = __uint_as_float(ra[2 * rep]), f1 = __uint_as_float(ra[2 * rep + 1]);
+            const float f2 = __uint_as_float(rb[2 * rep]), f3 = __uint_as_float(rb[2 * rep + 1]);
+            uint2* dst = reinterpret_cast<uint2*>(p.out + static_cast<long long>(row0 + m) * p.ldo + n);
+            if (plain) {  // the common case, kept free of the optional epilogues' code
+              uint2 pk;
+              if (has_bias) {
+                // Reference order: round the matmul to bf16, then add the bias in bf16.
+                const uint32_t r01 = cvt_bf16x2(f1, f0), r23 = cvt_bf16x2(f3, f2);
+                pk.x = cvt_bf16x2(bf16hi_f32(r01) + bias4[1], bf16lo_f32(r01) + bias4[0]);
+                pk.y = cvt_bf16x2(bf16hi_f32(r23) + bias4[3], bf16lo_f32(r23) + bias4[2]);
+              } else {
+                pk.x = cvt_bf16x2(f1, f0);
+                pk.y = cvt_bf16x2(f3, f2);
+              }
+              *dst = pk;
+            } else if (fused) {
+              fused_push4(p.peer, parity, static_cast<long long>(m) * p.N + n, f0, f1, f2, f3);
+            } else {
+              *dst = finish_row4(f0, f1, f2, f3, bias4, has_bias, p.epilogue);
+            }
           }
         }
       }
@@ -424,8 +442,6 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         // rows are sent at the end of the kernel, after a cluster barrier (a cluster CTA
         // has exactly this one tile segment, so the accumulator just stays where it is).
         pending_acc = b;
-        pending_wk = wk;
-        pending_nwk = nwk;
       } else {
         cluster_send(d_tmem, c, n_local, m_rows, wk, nwk);
         tc_fence_before();
@@ -465,7 +481,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         __syncwarp();
         if (lane == 0 && wk == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
         __threadfence();
-        named_bar_sync(nthr == kEpilogueThreads ? 1 : 2, nthr);
+        named_bar_sync(1, nthr);
         if (wtid == 0) atomicAdd(&p.counters[tile], 1);
       } else {
         // finisher: wait (bounded) until every contributor has published
@@ -474,7 +490,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           if (wait_flag_ge(&p.counters[tile], ncontrib, abortp))
             p.counters[tile] = 0;  // ready for the next launch / graph replay
         }
-        named_bar_sync(nthr == kEpilogueThreads ? 1 : 2, nthr);
+        named_bar_sync(1, nthr);
         if (*abortp) return false;
         for (int c0 = 16 * wk; c0 < p.NU; c0 += 16 * nwk) {
           float4 v[4];
@@ -526,20 +542,16 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     }
     return true;
   };
-  // Workers of the CTA's last segment: the epilogue warp and the four dequant warps of
-  // each lane quadrant.
-  constexpr int kLastWorkers = 1 + kAStages;
-  constexpr int kLastThreads = kEpilogueThreads + kAStages * kDequantThreads;
 
   if (warp == 0 || warp == 3) {
     // ============================================ TMA producer: packed weights
     // Two producer warps (0 and 3) take alternate units, which doubles the issue rate.
     // The whole warp runs the loop (so addresses and coordinates stay in uniform
-    // registers, which the TMA instruction wants); one elected lane issues.  The first
-    // pass over the ring was issued before the set-up barrier (see above).
+    // registers, which the TMA instruction wants); one elected lane issues.
     {
       bool ok = true;
-      for (int first = 2; first < (SW >> 1) && w_u < u_end; ++first) w_issue();  // rest of the first pass
+      // first pass over the ring: every stage is free
+      for (int first = 0; first < (SW >> 1) && w_u < u_end; ++first) w_issue();
       while (w_u < u_end) {
         ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarEmptyW + w_s), w_ph ^ 1u, abortp));
         if (!ok) break;
@@ -654,10 +666,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (leader) {
-          tc_commit(bar0 + 8 * (kBarAccFull + b));
-          if (u + nun == u_end) tc_commit(bar0 + 8 * kBarLast);  // wakes the helping dequant warps
-        }
+        if (leader) tc_commit(bar0 + 8 * (kBarAccFull + b));
         u += nun;
         ku0 = 0;
         if (++b == 2) { b = 0; accph ^= 1u; }
@@ -674,13 +683,12 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     while (u < u_end) {
       const int left = u_end - u;
       const int nun = left < (U - ku0) ? left : (U - ku0);
-      const bool last = (u + nun == u_end);  // the dequant warps join in (see below)
+      float bias4[4];
+      load_bias4(tile, bias4);
       if (!mbar_wait(bar0 + 8 * (kBarAccFull + b), accph, abortp)) break;
       if (etid == 0) DX_TRACE(0, tile - tile_begin);
       tc_fence_after();
-      if (!epilogue_segment(tile, ku0, nun, b, 0, last ? kLastWorkers : 1, etid,
-                            last ? kLastThreads : kEpilogueThreads))
-        break;
+      if (!epilogue_segment(tile, ku0, nun, b, bias4)) break;
       if (etid == 0) DX_TRACE(1, tile - tile_begin);
       u += nun;
       ku0 = 0;
@@ -865,20 +873,6 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       ku += kAStages;
       while (ku >= U) { ku -= U; ++tile; if (MULTI && ++ntile == p.tiles_n) ntile = 0; }
     }
-    // Nothing left to convert: help with the epilogue of the CTA's last segment, whose
-    // duration is pure tail latency (worker 1 + team of the quadrant's five).
-    if (ok) {
-      const int last_tile = (u_end - 1) / U;
-      const int seg = last_tile - tile_begin;            // index of the last segment
-      const int seg_u0 = seg == 0 ? u_begin : last_tile * U;
-      const int lb = seg & 1;                            // its accumulator
-      if (mbar_wait(bar0 + 8 * kBarLast, 0u, abortp)) {
-        tc_fence_after();
-        pdl_wait();  // outputs / scratch may still be in use by the previous kernel
-        epilogue_segment(last_tile, seg_u0 - last_tile * U, u_end - seg_u0, lb, 1 + team, kLastWorkers,
-                         kEpilogueThreads + (warp - 8) * 32 + lane, kLastThreads);
-      }
-    }
   }
 
   tc_fence_before();
@@ -911,7 +905,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       if (pending_acc >= 0) {
         tc_fence_after();
         cluster_send(tmem_addr(tmem0 + pending_acc * p.NU, 32 * (warp & 3), 0), lane & 3,
-                     32 * (warp & 3) + 4 * (lane >> 2), m_rows, pending_wk, pending_nwk);
+                     32 * (warp & 3) + 4 * (lane >> 2), m_rows, 0, 1);
         tc_fence_before();
       }
     }
@@ -944,9 +938,9 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
     }
     if (fused) {
-      // This CTA's rows of the tile are on their way to every rank: publish them, wait for
-      // the whole tile from every rank, then finish this CTA's rows from the local slots.
-      __threadfence_system();
+      // This CTA's rows of the tile are on their way to every rank: publish them (the
+      // barrier orders all stores before the signalling threads' cumulative release), wait
+      // for the whole tile from every rank, then finish this CTA's rows from the local slots.
       __syncthreads();
       if (threadIdx.x < p.peer.world && m_hi > m_lo) {  // a CTA without rows has nothing to do
         fused_signal(p.peer, ntile, threadIdx.x, static_cast<unsigned>(m_hi - m_lo));

@@ -80,7 +80,8 @@ def _worker(rank, world, port, results):
             y8 = fused.forward(x, ctx)
             torch.cuda.synchronize()
             fused.concurrent = True
-            assert torch.equal(y7, y8)  # same launches, same arithmetic, another schedule
+            # same linears on another schedule (the capped side-stream launch splits K differently)
+            results[rank + 6 * world] = y8.float().cpu().numpy()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 y9 = fused.forward(x, ctx)
@@ -116,7 +117,7 @@ def test_sharded_layer_set_matches_one_gpu(b200_lib, world):
     assert results.get("fused"), f"fused sum could not be set up: {results.get('fused_error')}"
     # NCCL all-reduce (plain, overlapped), peer kernel, fused q/k/v, rs+ag, fused sum: every
     # rank's output against the unsharded result
-    for slot in range(6 * world):
+    for slot in range(7 * world):
         e = np.abs(results[slot] - want).max() / max(np.abs(want).max(), 1e-6)
         assert e < 1e-2, (slot // world, slot % world, e)
     # every rank holds the same bits after the peer all-reduce and after the fused sum (fixed
