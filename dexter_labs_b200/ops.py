@@ -58,10 +58,11 @@ def _raise(code: int) -> None:
 _LAYOUTS = {"dexter": _lib.LAYOUT_DEXTER, "b200": _lib.LAYOUT_B200}
 _EPILOGUES = {None: _lib.EPILOGUE_NONE, "gelu_tanh": _lib.EPILOGUE_GELU_TANH}
 _need_cache: Dict[Tuple[int, int, int, int, int], int] = {}  # workspace bytes per problem
-
-
-def _raw_stream(device_index: int) -> int:
-    return torch._C._cuda_getCurrentRawStream(device_index)
+# (device, stream) -> (workspace tensor, its address, its size): see _workspace
+_ws_fast: Dict[Tuple[int, int], Tuple[torch.Tensor, int, int]] = {}
+_GEMM = _LIB.dxb_wq_gemm_ex
+_raw_stream = torch._C._cuda_getCurrentRawStream
+_current_device = torch.cuda.current_device
 
 
 def _run(bits: int, x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor,
@@ -74,11 +75,11 @@ def _run(bits: int, x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor
         raise RuntimeError("the B200 backend computes bf16 activations with bf16 scales only")
     if qweight.dtype != torch.uint8:
         raise ValueError("packed weights must be uint8")
-    k_dim = qweight.shape[0] * (2 if bits == 4 else 1)
-    *lead, k_in = x.shape
+    rows, n = qweight.shape
+    k_dim = rows * 2 if bits == 4 else rows
+    k_in = x.shape[-1]
     if k_in != k_dim:
         raise ValueError(f"x has K={k_in} but the packed weight has K={k_dim}")
-    n = qweight.shape[1]
     # A weight tensor that has to be copied here is written by the kernel right before the
     # GEMM on this stream, which the GEMM must then not overtake (it normally starts early
     # and reads its weights at once): such a call is launched in plain stream order.
@@ -94,16 +95,16 @@ def _run(bits: int, x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor
     if bias is not None and not bias.is_contiguous():
         bias, copied = bias.contiguous(), True
 
-    x2 = x.reshape(-1, k_in)
-    if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
+    x2 = x if x.dim() == 2 else x.reshape(-1, k_in)
+    if x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
         x2 = x2.contiguous()
     m = x2.shape[0]
-    out = torch.empty((m, n), device=x.device, dtype=x.dtype)
+    out = torch.empty((m, n), device=x.device, dtype=torch.bfloat16)
     if m == 0:
-        return out.view(*lead, n)
+        return out if x.dim() == 2 else out.view(*x.shape[:-1], n)
 
     dev = x.device.index
-    if dev != torch.cuda.current_device():
+    if dev != _current_device():
         with torch.cuda.device(dev):
             return _run(bits, x, qweight, scales, zeros, bias, group_size, max_ctas, layout=layout,
                         epilogue=epilogue, reduce=reduce)
@@ -115,26 +116,29 @@ def _run(bits: int, x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor
             copied = relaid[1]
             qweight, layout = relaid[0], "b200"
     stream = _raw_stream(dev)
+    ws = _ws_fast.get((dev, stream))
     key = (m, n, k_dim, bits, max_ctas)
     need = _need_cache.get(key)
     if need is None:
         need = _need_cache[key] = _LIB.dxb_workspace_bytes_ex(m, n, k_dim, bits, max_ctas)
-    ws = _workspace(x.device, stream, need)
+    if ws is None or ws[2] < need:
+        t = _workspace(x.device, stream, need)
+        ws = _ws_fast[(dev, stream)] = (t, t.data_ptr(), t.numel())
     opts = _lib.GemmOpts(_LAYOUTS[layout], _EPILOGUES[epilogue], max_ctas, 0, 0, None, 0, 1 if copied else 0)
     if reduce is not None:
         opts.peer_world, opts.peer_rank = reduce.world, reduce.rank
         opts.peer_regions, opts.peer_capacity_elems = reduce._ptrs, reduce.capacity
-    rc = _LIB.dxb_wq_gemm_ex(bits, x2.data_ptr(), x2.stride(0), qweight.data_ptr(), scales.data_ptr(),
-                             _ptr(zeros), _ptr(bias), out.data_ptr(), n, m, n, k_dim, group_size,
-                             ws.data_ptr(), ws.numel(), ctypes.byref(opts), ctypes.c_void_p(stream))
-    if rc != _lib.OK:
+    rc = _GEMM(bits, x2.data_ptr(), x2.stride(0), qweight.data_ptr(), scales.data_ptr(),
+               None if zeros is None else zeros.data_ptr(), None if bias is None else bias.data_ptr(),
+               out.data_ptr(), n, m, n, k_dim, group_size, ws[1], ws[2], opts, stream)
+    if rc != 0:
         _raise(rc)
     if _CHECK:
-        code = _LIB.dxb_read_status(ws.data_ptr(), ctypes.c_void_p(stream))
+        code = _LIB.dxb_read_status(ws[1], ctypes.c_void_p(stream))
         if code != _lib.OK:
-            ws.zero_()
+            ws[0].zero_()
             _raise(code)
-    return out.view(*lead, n)
+    return out if x.dim() == 2 else out.view(*x.shape[:-1], n)
 
 
 _CHECK = bool(os.environ.get("DEXTER_B200_CHECK"))
