@@ -171,11 +171,7 @@ struct WqParams {
 // tanh-GELU of a value that has already been rounded to bf16, as the reference applies it
 // between the FFN linears (torch gelu(approximate="tanh") on the bf16 output of the up
 // projection, python/dexter/models/dreamzero/model.py:279-285): evaluated in fp32, rounded once.
-#ifdef DXB_GELU_NOINLINE
-__device__ __noinline__ float gelu_tanh(float v) {
-#else
 __device__ __forceinline__ float gelu_tanh(float v) {
-#endif
   const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
   return 0.5f * v * (1.0f + tanhf(inner));
 }
