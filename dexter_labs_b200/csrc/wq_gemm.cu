@@ -198,7 +198,18 @@ __device__ __forceinline__ uint2 finish_row4(float f0, float f1, float f2, float
 // pair.  The single-block kernel carries none of that bookkeeping.
 // RELAID (int4 only): the packed bytes were rewritten by wq_relayout_w4_kernel so that one
 // 32-bit word holds the k-pairs the TMEM store wants (see there); saves the byte permutes.
-template <int BITS, bool HAS_ZERO, bool MULTI, bool RELAID>
+// MODE: the same pipeline compiled three times.  The two lean instances carry only what the
+// common launches execute, which keeps their code a third of the general instance's: these
+// launches last 8-15 us, and a kernel whose code is larger than the instruction cache pays for
+// fetching it again in every launch (measured: 12.6 against 13.5 us on the headline shape).
+//   kModeGeneral  every epilogue (activation, sum over ranks), tiles shared between CTAs
+//                 through global partial sums, clusters
+//   kModeWhole    whole tiles per CTA, plain epilogue (optional bias), no cluster
+//   kModeCluster  one tile per cluster (K split, sum through distributed shared memory),
+//                 plain epilogue
+enum : int { kModeGeneral = 0, kModeWhole = 1, kModeCluster = 2 };
+
+template <int BITS, bool HAS_ZERO, bool MULTI, bool RELAID, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_x,
            const WqParams p) {
@@ -230,15 +241,18 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const int TU = p.total_units;
   const int G = static_cast<int>(gridDim.x);
   const int U = p.units_per_tile;
-  const int C = p.cluster;
-  const int crank = C > 1 ? static_cast<int>(blockIdx.x % C) : 0;
-  const int ctile = C > 1 ? static_cast<int>(blockIdx.x / C) : 0;
-  const int u_begin = C > 1 ? ctile * U + crank * U / C
-                      : p.tile_ranges ? static_cast<int>(range_begin(blockIdx.x, p.tiles, G)) * U
-                                      : static_cast<int>(range_begin(blockIdx.x, TU, G));
-  const int u_end = C > 1 ? ctile * U + (crank + 1) * U / C
-                    : p.tile_ranges ? static_cast<int>(range_begin(blockIdx.x + 1, p.tiles, G)) * U
-                                    : static_cast<int>(range_begin(blockIdx.x + 1, TU, G));
+  constexpr bool kLean = MODE != kModeGeneral;
+  const int C = MODE == kModeWhole ? 1 : p.cluster;  // kModeCluster is only launched with C > 1
+  const bool clustered = MODE == kModeCluster || (MODE == kModeGeneral && C > 1);
+  const bool tile_ranges = MODE == kModeWhole || (MODE == kModeGeneral && p.tile_ranges);
+  const int crank = clustered ? static_cast<int>(blockIdx.x % C) : 0;
+  const int ctile = clustered ? static_cast<int>(blockIdx.x / C) : 0;
+  const int u_begin = clustered ? ctile * U + crank * U / C
+                      : tile_ranges ? static_cast<int>(range_begin(blockIdx.x, p.tiles, G)) * U
+                                    : static_cast<int>(range_begin(blockIdx.x, TU, G));
+  const int u_end = clustered ? ctile * U + (crank + 1) * U / C
+                    : tile_ranges ? static_cast<int>(range_begin(blockIdx.x + 1, p.tiles, G)) * U
+                                  : static_cast<int>(range_begin(blockIdx.x + 1, TU, G));
   const int tile_begin = u_begin / U;
   const int ku_begin = u_begin - tile_begin * U;
 
@@ -349,7 +363,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const int g = lane >> 2;
     const int n_local = 32 * q + 4 * g;
     const bool has_bias = p.bias != nullptr;
-    const bool whole = (nun == U);
+    const bool whole = MODE == kModeWhole || (MODE == kModeGeneral && nun == U);
     const int tblock = MULTI ? tile / p.tiles_n : 0;  // token block of this tile
     const int ntile = tile - tblock * p.tiles_n;      // its 128 weight columns
     const int row0 = tblock * 128;
@@ -358,8 +372,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const bool n_ok = n < p.N;
     // Sum over ranks fused into this launch (one token block only): finished rows go to
     // every rank's receive buffer instead of `out`; fused_finish then completes the tile.
-    const bool fused = p.peer.world > 1;
-    const bool plain = !fused && p.epilogue == DXB_EPILOGUE_NONE;
+    const bool fused = !kLean && p.peer.world > 1;
+    const bool plain = kLean || (!fused && p.epilogue == DXB_EPILOGUE_NONE);
     const unsigned parity =
         fused ? (__ldcg(reinterpret_cast<const unsigned*>(p.peer.region[p.peer.rank])) & 1u) : 0u;
     auto fused_finish = [&]() -> bool {
@@ -428,7 +442,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       __syncwarp();
       if (lane == 0 && wk == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
       if (fused && !fused_finish()) return false;
-    } else if (C > 1) {
+    } else if (clustered) {
       // Cluster mode: CTA r of the cluster finishes token rows [r*rows_per, (r+1)*rows_per)
       // of the tile.  Every CTA sends each owner its fp32 partial rows straight from the
       // accumulator registers into the owner's receive buffer `crank` (distributed shared
@@ -444,7 +458,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         __syncwarp();
         if (lane == 0 && wk == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
       }
-    } else {
+    } else if (!kLean) {
       // A tile shared by several CTAs (equal unit ranges cut it): the CTA that holds the
       // tile's first units finishes it.  Ranges are contiguous and worked through in
       // order, so a CTA contributes to a tile it does not finish as its FIRST segment
@@ -873,7 +887,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   tc_fence_before();
   __syncthreads();
-  if (C > 1) {
+  if (clustered) {
     // The cluster's tile: token block and column tile.
     const int tblock = MULTI ? ctile / p.tiles_n : 0;
     const int ntile = ctile - tblock * p.tiles_n;
@@ -910,7 +924,8 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // remote is touched any more, so CTAs leave independently.
     cluster_sync_all();
     pdl_wait();
-    const bool fused = p.peer.world > 1;
+    const bool fused = !kLean && p.peer.world > 1;
+    const int epi = kLean ? static_cast<int>(DXB_EPILOGUE_NONE) : p.epilogue;
     const unsigned parity =
         fused ? (__ldcg(reinterpret_cast<const unsigned*>(p.peer.region[p.peer.rank])) & 1u) : 0u;
     if (n < p.N) {
@@ -930,7 +945,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           fused_push4(p.peer, parity, static_cast<long long>(m_lo + j) * p.N + n, acc.x, acc.y, acc.z, acc.w);
         else
           *reinterpret_cast<uint2*>(p.out + static_cast<long long>(row0 + m_lo + j) * p.ldo + n) =
-              finish_row4(acc.x, acc.y, acc.z, acc.w, bias4, has_bias, p.epilogue);
+              finish_row4(acc.x, acc.y, acc.z, acc.w, bias4, has_bias, epi);
       }
     }
     if (fused) {
@@ -948,12 +963,12 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           const int m = m_lo + (i >> 5);
           const float4 a = fused_sum4(p.peer, parity, static_cast<long long>(m) * p.N + n);
           *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.ldo + n) =
-              finish_row4(a.x, a.y, a.z, a.w, bias4, has_bias, p.epilogue);
+              finish_row4(a.x, a.y, a.z, a.w, bias4, has_bias, epi);
         }
       }
     }
   }
-  if (p.peer.world > 1) {
+  if (!kLean && p.peer.world > 1) {
     // The last CTA to leave moves the per-tile row baselines and the epoch on for the next
     // call (every other CTA has finished reading them by then).
     __shared__ int is_last;
@@ -1288,6 +1303,24 @@ static const CUtensorMap* cached_map(const MapKey& key, Encode&& encode) {
   return &cache.emplace(key, m).first->second;
 }
 
+using TcKernel = void (*)(const CUtensorMap, const CUtensorMap, const WqParams);
+
+template <int BITS, bool HAS_ZERO, bool MULTI, bool RELAID>
+static TcKernel pick_mode(int mode) {
+  switch (mode) {
+    case kModeWhole: return wq_gemm_tc<BITS, HAS_ZERO, MULTI, RELAID, kModeWhole>;
+    case kModeCluster: return wq_gemm_tc<BITS, HAS_ZERO, MULTI, RELAID, kModeCluster>;
+    default: return wq_gemm_tc<BITS, HAS_ZERO, MULTI, RELAID, kModeGeneral>;
+  }
+}
+
+template <int BITS, bool HAS_ZERO>
+static TcKernel pick_kernel(bool multi, bool relaid, int mode) {
+  if (BITS == 4 && relaid)
+    return multi ? pick_mode<BITS, HAS_ZERO, true, BITS == 4>(mode) : pick_mode<BITS, HAS_ZERO, false, BITS == 4>(mode);
+  return multi ? pick_mode<BITS, HAS_ZERO, true, false>(mode) : pick_mode<BITS, HAS_ZERO, false, false>(mode);
+}
+
 template <int BITS, bool HAS_ZERO>
 static int launch_tc(const void* x, long long ldx, const void* qw, const void* scales,
                      const void* zeros, const void* bias, void* out, long long ldo, int M, int N,
@@ -1311,19 +1344,17 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
     auto set = [&](auto kern) {
       ok = ok && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024) == cudaSuccess;
     };
-    set(wq_gemm_tc<BITS, HAS_ZERO, true, false>);
-    set(wq_gemm_tc<BITS, HAS_ZERO, false, false>);
-    if (BITS == 4) {
-      set(wq_gemm_tc<BITS, HAS_ZERO, true, BITS == 4>);
-      set(wq_gemm_tc<BITS, HAS_ZERO, false, BITS == 4>);
-    }
+    for (int multi = 0; multi < 2; ++multi)
+      for (int relaid = 0; relaid < (BITS == 4 ? 2 : 1); ++relaid)
+        for (int mode = 0; mode < 3; ++mode) set(pick_kernel<BITS, HAS_ZERO>(multi, relaid, mode));
     if (!ok) return DXB_ERR_CUDA;
     attr_dev = dev;
   }
   const bool multi = plp->tiles > plp->tiles_n;
   const bool relaid = BITS == 4 && opts.relaid;
-  auto kernel = multi ? (relaid ? wq_gemm_tc<BITS, HAS_ZERO, true, BITS == 4> : wq_gemm_tc<BITS, HAS_ZERO, true, false>)
-                      : (relaid ? wq_gemm_tc<BITS, HAS_ZERO, false, BITS == 4> : wq_gemm_tc<BITS, HAS_ZERO, false, false>);
+  // The lean instances serve the plain epilogue; which of the two follows from the plan below.
+  const bool lean = opts.epilogue == DXB_EPILOGUE_NONE && opts.peer.world <= 1;
+  auto kernel = pick_kernel<BITS, HAS_ZERO>(multi, relaid, lean ? kModeCluster : kModeGeneral);
 
   // Few tiles: split each tile's K range over a thread-block cluster (<= 8 CTAs) that
   // reduces through distributed shared memory.  The cluster size is the largest one for
@@ -1335,7 +1366,7 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
     const long long key = (static_cast<long long>(dev) << 48) ^ (static_cast<long long>(plp->tiles) << 28) ^
                           (static_cast<long long>(plp->units_per_tile) << 8) ^ static_cast<long long>(plp->NU >> 4) ^
                           (static_cast<long long>(budget) << 38) ^ (static_cast<long long>(multi) << 58) ^
-                          (static_cast<long long>(relaid) << 59);
+                          (static_cast<long long>(relaid) << 59) ^ (static_cast<long long>(lean) << 60);
     auto it = cache.find(key);
     if (it != cache.end()) {
       cluster = it->second;
@@ -1376,6 +1407,8 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
     }
   }
   const Plan& pl = *plp;
+  if (cluster == 1)
+    kernel = pick_kernel<BITS, HAS_ZERO>(multi, relaid, lean && pl.whole ? kModeWhole : kModeGeneral);
 
   const CUtensorMap* tq = cached_map(MapKey{qw, N, pl.rows, 0, BITS}, [&](CUtensorMap* m) {
     const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(pl.rows)};
