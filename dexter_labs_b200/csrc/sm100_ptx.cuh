@@ -159,6 +159,18 @@ __device__ __forceinline__ float4 ld_smem_f4(uint32_t addr) {
 }
 // Hardware barrier over every thread of the cluster; release/acquire at cluster scope,
 // so shared-memory writes made before it are visible to peer CTAs after it.
+// Rank of this CTA in its cluster and index of the cluster in the grid (x), read from the
+// special registers: no division by the cluster size.
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");

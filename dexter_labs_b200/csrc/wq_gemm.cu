@@ -162,6 +162,8 @@ struct WqParams {
   int rows_inv;        // ceil(65536 / rows_per): row / rows_per == (row * rows_inv) >> 16
   int epilogue;        // DXB_EPILOGUE_*: what is applied to the bf16 result before it is stored
   int tile_ranges;     // CTAs take whole tiles (ranges cut in tiles, not in units)
+  int range_q, range_r;  // quotient and remainder of the cut: units of a tile by the cluster
+                         // size, or tiles by the grid size (see the kernel's range arithmetic)
   PeerFuse peer;       // peer.world > 1: the sum over ranks is part of this launch (see below)
   long long* trace;    // only used when built with -DDXB_TRACE
   int debug;           // -DDXB_TRACE builds only: parts of the pipeline to leave out (timing experiments)
@@ -220,11 +222,16 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   constexpr int UNIT_ROWS = BITS == 4 ? 64 : 128;   // packed rows per unit
   constexpr int W_STAGE = UNIT_ROWS * kTileN;       // bytes of one packed-weight stage
 
+#ifdef DXB_TRACE
+  const long long t_entry = clock64();
+#endif
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[kNumBars];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
+#ifdef DXB_TRACE
   __shared__ long long t_start;
+#endif
 
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t w_ring = smem0;
@@ -245,21 +252,28 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   const int C = MODE == kModeWhole ? 1 : p.cluster;  // kModeCluster is only launched with C > 1
   const bool clustered = MODE == kModeCluster || (MODE == kModeGeneral && C > 1);
   const bool tile_ranges = MODE == kModeWhole || (MODE == kModeGeneral && p.tile_ranges);
-  const int crank = clustered ? static_cast<int>(blockIdx.x % C) : 0;
-  const int ctile = clustered ? static_cast<int>(blockIdx.x / C) : 0;
-  const int u_begin = clustered ? ctile * U + crank * U / C
-                      : tile_ranges ? static_cast<int>(range_begin(blockIdx.x, p.tiles, G)) * U
-                                    : static_cast<int>(range_begin(blockIdx.x, TU, G));
-  const int u_end = clustered ? ctile * U + (crank + 1) * U / C
-                    : tile_ranges ? static_cast<int>(range_begin(blockIdx.x + 1, p.tiles, G)) * U
-                                  : static_cast<int>(range_begin(blockIdx.x + 1, TU, G));
-  const int tile_begin = u_begin / U;
-  const int ku_begin = u_begin - tile_begin * U;
+  // Ranges without a division on the way to the first weight load (a 64-bit division is a few
+  // hundred cycles at the head of every launch): `range_q`, `range_r` are quotient and remainder
+  // of what is being cut (a cluster's units by its size, or the tiles by the grid), so part i
+  // starts at i * q + min(i, r).  Only unit ranges that cut tiles still divide.
+  const int crank = clustered ? static_cast<int>(cluster_cta_rank()) : 0;
+  const int ctile = clustered ? static_cast<int>(cluster_id_x()) : 0;
+  const int part = clustered ? crank : static_cast<int>(blockIdx.x);
+  const int cut_begin = part * p.range_q + (part < p.range_r ? part : p.range_r);
+  const int cut_end = cut_begin + p.range_q + (part < p.range_r ? 1 : 0);
+  const bool unit_ranges = MODE == kModeGeneral && !clustered && !tile_ranges;
+  const int u_begin = clustered ? ctile * U + cut_begin
+                      : !unit_ranges ? cut_begin * U : static_cast<int>(range_begin(blockIdx.x, TU, G));
+  const int u_end = clustered ? ctile * U + cut_end
+                    : !unit_ranges ? cut_end * U : static_cast<int>(range_begin(blockIdx.x + 1, TU, G));
+  const int tile_begin = clustered ? ctile : !unit_ranges ? cut_begin : u_begin / U;
+  const int ku_begin = clustered ? cut_begin : !unit_ranges ? 0 : u_begin - tile_begin * U;
 
   // Packed-weight producers (warps 0 and 3, alternate units): cursor of the next unit to load.
-  // (Issuing the first loads before the CTA-wide set-up barrier, triggering the dependent
-  // launch earlier, and staggering the teams' first conversions were all measured: each
-  // made the launch slightly slower, so the plain order stays.)
+  // (Issuing the first loads before the CTA-wide set-up barrier, with the producers only
+  // arriving at it, triggering the dependent launch earlier, staggering the teams' first
+  // conversions, and a first conversion pass that only walks the code to fill the
+  // instruction cache were all measured: none made the launch faster, so the plain order stays.)
   const int wp = warp == 0 ? 0 : 1;
   int w_u = u_begin + wp, w_tile = tile_begin, w_ku = ku_begin + wp, w_s = wp, w_ntile = 0;
   uint32_t w_ph = 0;
@@ -282,15 +296,26 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   };
   if (warp == 0 || warp == 3) {
     if (lane == 0) tma_prefetch_desc(&tm_q);
-    // full_w barriers of this producer's stages (even stages: warp 0, odd: warp 3); warp 3
-    // also initialises every other barrier, which nobody touches before the barrier below
-    for (int i = wp + 2 * lane; i < kBarEmptyW; i += 64) mbar_init(bar0 + 8 * i, bar_count(i));
-    if (warp == 3) {
-      for (int i = kBarEmptyW + lane; i < kNumBars; i += 32) mbar_init(bar0 + 8 * i, bar_count(i));
-      if (lane == 0) {
-        t_start = clock64();
-        abort_flag = 0;
+    // Each producer initialises the full and empty barriers of its own stages (even stages:
+    // warp 0, odd: warp 3), the only ones it ever waits on, so it needs nobody else's set-up;
+    // warp 3 also initialises the remaining barriers, which nobody touches before the set-up
+    // barrier below.  Both clear the abort flag (same value) before anybody can wait.
+    static_assert(kBarEmptyW - kBarFullW == 16 && kBarReady - kBarEmptyW == 16 && kNumBars - kBarReady <= 24,
+                  "one lane per barrier below");
+    if (lane < 8) {
+      mbar_init(bar0 + 8 * (kBarFullW + wp + 2 * lane), bar_count(kBarFullW + wp + 2 * lane));
+      mbar_init(bar0 + 8 * (kBarEmptyW + wp + 2 * lane), bar_count(kBarEmptyW + wp + 2 * lane));
+    } else if (warp == 3 && kBarReady + lane - 8 < kNumBars) {
+      mbar_init(bar0 + 8 * (kBarReady + lane - 8), bar_count(kBarReady + lane - 8));
+    }
+    if (lane == 0) {
+      abort_flag = 0;
+#ifdef DXB_TRACE
+      if (warp == 3) {
+        t_start = t_entry;  // trace builds: every stamp counts from the thread's first instruction
+        DX_TRACE(5, 0);     // barriers initialised
       }
+#endif
     }
     mbar_init_fence();
     __syncwarp();
@@ -306,6 +331,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem0 = tmem_base_s;
+  if (threadIdx.x == 0) DX_TRACE(5, 1);  // set-up barrier passed
   // The next kernel of the stream may start now: its weight loads and conversion do not
   // depend on this kernel; it waits (pdl_wait) before it touches activations or outputs.
   pdl_launch_dependents();
@@ -561,7 +587,10 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     {
       bool ok = true;
       // first pass over the ring: every stage is free
-      for (int first = 0; first < (SW >> 1) && w_u < u_end; ++first) w_issue();
+      for (int first = 0; first < (SW >> 1) && w_u < u_end; ++first) {
+        w_issue();
+        if (warp == 0 && lane == 0 && first == 0) DX_TRACE(5, 2);  // first weight load issued
+      }
       while (w_u < u_end) {
         ok = __all_sync(0xffffffffu, mbar_wait(bar0 + 8 * (kBarEmptyW + w_s), w_ph ^ 1u, abortp));
         if (!ok) break;
@@ -578,6 +607,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     // ============================================== TMA producer: activations
     // Activations may be the output of the previous kernel in the stream.
     pdl_wait();
+    if (lane == 0) DX_TRACE(5, 3);  // the previous kernel of the stream is complete
     {
       int ku = ku_begin, t = 0;
       int ntile = MULTI ? tile_begin % p.tiles_n : 0;
@@ -645,6 +675,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (int i = 0; i < nun; ++i) {
           if (!mbar_wait(bar0 + 8 * (kBarReady + t), ph, abortp)) { ok = false; break; }
           tc_fence_after();
+          if (lane == 0 && done == 0) DX_TRACE(5, 4);  // first unit ready (weights in TMEM, activations in smem)
           if (leader && DX_DEBUG(32)) {
             // experiment: the two planes accumulate into different accumulators, alternating
             const uint32_t d2 = tmem0 + (b ^ 1) * p.NU;
@@ -759,7 +790,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
     };
     if (u < u_end) load_sz(tile, MULTI ? ntile : tile, ku, sc_nx, zr_nx);
-    for (; u < u_end; u += kAStages) {
+    while (u < u_end) {
 #pragma unroll
       for (int pl = 0; pl < PLANES; ++pl) { sc[pl] = sc_nx[pl]; if (HAS_ZERO) zr[pl] = zr_nx[pl]; }
       {
@@ -882,6 +913,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       if (s >= SW) { s -= SW; ph ^= 1u; }
       ku += kAStages;
       while (ku >= U) { ku -= U; ++tile; if (MULTI && ++ntile == p.tiles_n) ntile = 0; }
+      u += kAStages;
     }
   }
 
@@ -1472,6 +1504,12 @@ static int launch_tc(const void* x, long long ldx, const void* qw, const void* s
   p.recv_off = pl.recv_off;
   p.recv_alias = cluster > 1 ? pl.recv_alias : 0;
   p.rows_per = ((M > 128 ? 128 : M) + cluster - 1) / cluster;  // token rows of one block per CTA
+  {
+    const int what = cluster > 1 ? pl.units_per_tile : pl.tiles;
+    const int parts = cluster > 1 ? cluster : pl.ctas;
+    p.range_q = what / parts;
+    p.range_r = what % parts;
+  }
   p.rows_inv = (65536 + p.rows_per - 1) / p.rows_per;
 
   cudaLaunchConfig_t cfg = {};

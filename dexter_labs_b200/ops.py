@@ -58,6 +58,7 @@ def _raise(code: int) -> None:
 _LAYOUTS = {"dexter": _lib.LAYOUT_DEXTER, "b200": _lib.LAYOUT_B200}
 _EPILOGUES = {None: _lib.EPILOGUE_NONE, "gelu_tanh": _lib.EPILOGUE_GELU_TANH}
 _need_cache: Dict[Tuple[int, int, int, int, int], int] = {}  # workspace bytes per problem
+_opts_cache: Dict[tuple, "_lib.GemmOpts"] = {}  # option structs of calls without a fused sum
 # (device, stream) -> (workspace tensor, its address, its size): see _workspace
 _ws_fast: Dict[Tuple[int, int], Tuple[torch.Tensor, int, int]] = {}
 _GEMM = _LIB.dxb_wq_gemm_ex
@@ -124,10 +125,15 @@ def _run(bits: int, x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor
     if ws is None or ws[2] < need:
         t = _workspace(x.device, stream, need)
         ws = _ws_fast[(dev, stream)] = (t, t.data_ptr(), t.numel())
-    opts = _lib.GemmOpts(_LAYOUTS[layout], _EPILOGUES[epilogue], max_ctas, 0, 0, None, 0, 1 if copied else 0)
-    if reduce is not None:
-        opts.peer_world, opts.peer_rank = reduce.world, reduce.rank
-        opts.peer_regions, opts.peer_capacity_elems = reduce._ptrs, reduce.capacity
+    if reduce is None:
+        okey = (layout, epilogue, max_ctas, copied)
+        opts = _opts_cache.get(okey)  # read-only for the library: one struct per combination
+        if opts is None:
+            opts = _opts_cache[okey] = _lib.GemmOpts(_LAYOUTS[layout], _EPILOGUES[epilogue], max_ctas, 0, 0,
+                                                     None, 0, 1 if copied else 0)
+    else:
+        opts = _lib.GemmOpts(_LAYOUTS[layout], _EPILOGUES[epilogue], max_ctas, reduce.world, reduce.rank,
+                             reduce._ptrs, reduce.capacity, 1 if copied else 0)
     rc = _GEMM(bits, x2.data_ptr(), x2.stride(0), qweight.data_ptr(), scales.data_ptr(),
                None if zeros is None else zeros.data_ptr(), None if bias is None else bias.data_ptr(),
                out.data_ptr(), n, m, n, k_dim, group_size, ws[1], ws[2], opts, stream)
