@@ -359,7 +359,6 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
     }
   };
-  int pending_acc = -1;  // cluster mode with aliased receive buffers: accumulator still to be sent
 
   // ------------------------------------------------------------------ epilogue of one segment
   // A segment = this CTA's units of one tile, summed in accumulator `b`; run by the four
@@ -473,17 +472,10 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       // of the tile.  Every CTA sends each owner its fp32 partial rows straight from the
       // accumulator registers into the owner's receive buffer `crank` (distributed shared
       // memory stores); one cluster barrier later the owner only reads its own memory.
-      if (p.recv_alias) {
-        // The receive buffers lie over the rings, which the peers may still be using: the
-        // rows are sent at the end of the kernel, after a cluster barrier (a cluster CTA
-        // has exactly this one tile segment, so the accumulator just stays where it is).
-        pending_acc = b;
-      } else {
-        cluster_send(d_tmem, c, n_local, m_rows, wk, nwk);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0 && wk == 0) mbar_arrive(bar0 + 8 * (kBarAccEmpty + b));
-      }
+      // A cluster CTA has exactly this one segment, in accumulator 0, at the very end of its
+      // work, when every other warp is idle: the accumulator stays where it is and ALL warps
+      // send it after the CTA-wide barrier below (six warps per TMEM lane quadrant, 16
+      // token columns each, instead of the four epilogue warps walking all of them).
     } else if (!kLean) {
       // A tile shared by several CTAs (equal unit ranges cut it): the CTA that holds the
       // tile's first units finishes it.  Ranges are contiguous and worked through in
@@ -941,16 +933,16 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       bias4[2] = bf16lo_f32(bb.y); bias4[3] = bf16hi_f32(bb.y);
     }
     if (p.recv_alias) {
-      // Every CTA of the cluster is past its main loop after this barrier: nothing reads or
-      // writes the rings any more, so the receive buffers that lie over them may be filled.
+      // The receive buffers lie over the rings, which the peers may still be using.  Every
+      // CTA of the cluster is past its main loop after this barrier: nothing reads or writes
+      // the rings any more, so the buffers may be filled.
       cluster_sync_all();
-      if (pending_acc >= 0) {
-        tc_fence_after();
-        cluster_send(tmem_addr(tmem0 + pending_acc * p.NU, 32 * (warp & 3), 0), lane & 3,
-                     32 * (warp & 3) + 4 * (lane >> 2), m_rows, 0, 1);
-        tc_fence_before();
-      }
     }
+    // The epilogue warps have seen the accumulator complete before the CTA-wide barrier above.
+    tc_fence_after();
+    cluster_send(tmem_addr(tmem0, 32 * (warp & 3), 0), lane & 3, 32 * (warp & 3) + 4 * (lane >> 2), m_rows,
+                 warp >> 2, kThreads / 128);
+    tc_fence_before();
     // After this barrier every partial row of this CTA's share has arrived in its receive
     // buffers: sum them in rank order (deterministic), add the bias, write bf16.  Nothing
     // remote is touched any more, so CTAs leave independently.
