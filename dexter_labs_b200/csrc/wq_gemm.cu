@@ -347,6 +347,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       tmem_ld_16x128b_x4(d_tmem + c0, ra);
       tmem_ld_16x128b_x4(d_tmem + (16u << 16) + c0, rb);
       tc_wait_ld();
+      if (threadIdx.x == 0) DX_TRACE(7, 7);  // accumulator chunk in registers
 #pragma unroll
       for (int rep = 0; rep < 4; ++rep) {
         const int m = c0 + 4 * rep + c;
@@ -911,6 +912,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) DX_TRACE(7, 1);  // every role is through its loop
   if (clustered) {
     // The cluster's tile: token block and column tile.
     const int tblock = MULTI ? ctile / p.tiles_n : 0;
@@ -940,14 +942,18 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     }
     // The epilogue warps have seen the accumulator complete before the CTA-wide barrier above.
     tc_fence_after();
+    if (threadIdx.x == 0) DX_TRACE(7, 6);  // about to send
     cluster_send(tmem_addr(tmem0, 32 * (warp & 3), 0), lane & 3, 32 * (warp & 3) + 4 * (lane >> 2), m_rows,
                  warp >> 2, kThreads / 128);
     tc_fence_before();
+    if (threadIdx.x == 0) DX_TRACE(7, 2);  // partial sums sent
     // After this barrier every partial row of this CTA's share has arrived in its receive
     // buffers: sum them in rank order (deterministic), add the bias, write bf16.  Nothing
     // remote is touched any more, so CTAs leave independently.
     cluster_sync_all();
+    if (threadIdx.x == 0) DX_TRACE(7, 3);  // cluster barrier passed
     pdl_wait();
+    if (threadIdx.x == 0) DX_TRACE(7, 4);  // previous kernel complete
     const bool fused = !kLean && p.peer.world > 1;
     const int epi = kLean ? static_cast<int>(DXB_EPILOGUE_NONE) : p.epilogue;
     const unsigned parity =
@@ -972,6 +978,7 @@ wq_gemm_tc(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
               finish_row4(acc.x, acc.y, acc.z, acc.w, bias4, has_bias, epi);
       }
     }
+    if (threadIdx.x == 0) DX_TRACE(7, 5);  // rows summed and stored
     if (fused) {
       // This CTA's rows of the tile are on their way to every rank: publish them (the
       // barrier orders all stores before the signalling threads' cumulative release), wait
