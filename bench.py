@@ -582,7 +582,7 @@ def run_ours(args) -> int:
                      "frac": achieved / peak, "traffic": bytes_per_launch * DRAM_OVER_ALGORITHMIC,
                      "traffic_source": "algorithmic bytes x 1.025 (DRAM / algorithmic ratio of one ncu capture "
                                        "of the headline launch); scaled, not measured in this run",
-                     "kernel": "wq_gemm_tc<4,false,false,true>",
+                     "kernel": "wq_gemm_tc<4,false,false,true,kModeWhole/kModeCluster>",
                      "peak_source": f"{peaks['source']} ({'sustained' if sustained else 'burst'})",
                      "algorithmic_bytes_per_launch": bytes_per_launch,
                      "algorithmic_flops_per_launch": flops_per_launch,
