@@ -26,7 +26,16 @@ def _worker(rank, world, port, results):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        from dexter_labs_b200 import tp
+        from dexter_labs_b200 import ops, tp
+
+        def settled(phase):
+            # No kernel of this phase gave up on a bounded wait; then line the ranks up again: a
+            # kernel waits about a second for a peer, and eight eagerly launching processes
+            # that also pickle results between phases must not drift further apart than that.
+            torch.cuda.synchronize()
+            code = ops.last_status()
+            assert code == 0, (phase, rank, code)
+            dist.barrier()
 
         ls = tp.LayerSet.build("5b", blocks=1, rank=rank, world=world, seed=3, device=f"cuda:{rank}")
         torch.manual_seed(1)
@@ -58,6 +67,7 @@ def _worker(rank, world, port, results):
             results["peer"] = True
         else:
             results["peer_error"] = getattr(ls, "_peer_error", "unknown")
+        settled("all-reduce and peer kernel")
         # q/k/v fused into one launch, cross k/v overlapped with self o's collective
         fused = tp.LayerSet.build("5b", blocks=1, rank=rank, world=world, seed=3, device=f"cuda:{rank}",
                                   fuse_qkv=True, concurrent=True, collective="all_reduce")
@@ -72,27 +82,27 @@ def _worker(rank, world, port, results):
         results[rank + 4 * world] = y6.float().cpu().numpy()
         # the sum over ranks inside the row-parallel GEMM's own launch: plain and overlapped
         # schedules, eagerly and as a replayed CUDA graph
+        settled("fused q/k/v and reduce-scatter + all-gather")
         if fused.enable_fused_reduce(83, f"cuda:{rank}"):
             y7 = fused.forward(x, ctx)
-            torch.cuda.synchronize()
+            settled("fused sum, overlapped schedule, eager")
             results[rank + 5 * world] = y7.float().cpu().numpy()
             fused.concurrent = False
+            dist.barrier()
             y8 = fused.forward(x, ctx)
-            torch.cuda.synchronize()
+            settled("fused sum, one stream, eager")
             fused.concurrent = True
             # same linears on another schedule (the capped side-stream launch splits K differently)
             results[rank + 6 * world] = y8.float().cpu().numpy()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 y9 = fused.forward(x, ctx)
-            for _ in range(3):
+            for i in range(3):
                 y9.zero_()
+                dist.barrier()
                 graph.replay()
-                torch.cuda.synchronize()
+                settled(f"fused sum, replayed graph {i}")
                 assert torch.equal(y9, y7)
-            from dexter_labs_b200 import ops
-
-            assert ops.last_status() == 0
             results["fused"] = True
         else:
             results["fused_error"] = getattr(fused, "_peer_error", "unknown")
