@@ -86,5 +86,17 @@ def load() -> ctypes.CDLL:
     return lib
 
 
+def load_fast():
+    """``_dxb_fast.gemm`` bound to this library's ``dxb_wq_gemm_ex``, or None when the compiled
+    binding has not been built (the ctypes path then serves every call)."""
+    lib = load()
+    try:
+        from . import _dxb_fast
+    except ImportError:
+        return None
+    _dxb_fast.bind(ctypes.cast(lib.dxb_wq_gemm_ex, ctypes.c_void_p).value)
+    return _dxb_fast.gemm
+
+
 def strerror(code: int) -> str:
     return load().dxb_strerror(code).decode()

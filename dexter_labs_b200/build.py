@@ -11,12 +11,16 @@ import os
 import shutil
 import subprocess
 import sys
+import sysconfig
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
 SOURCES = [PKG_DIR / "csrc" / "wq_gemm.cu", PKG_DIR / "csrc" / "peer_reduce.cu"]
 HEADERS = [PKG_DIR / "csrc" / "sm100_ptx.cuh", PKG_DIR / "csrc" / "wq_common.cuh", PKG_DIR.parent / "include" / "dexter_b200.h"]
 LIB_PATH = PKG_DIR / "libdexter_b200.so"
+# compiled CPython binding of the hot call (csrc/fastcall.c); plain C, no CUDA
+FAST_SOURCE = PKG_DIR / "csrc" / "fastcall.c"
+FAST_PATH = PKG_DIR / ("_dxb_fast" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -39,8 +43,33 @@ def is_stale() -> bool:
     return any(src.stat().st_mtime > built for src in SOURCES + HEADERS if src.exists())
 
 
+def fast_is_stale() -> bool:
+    if not FAST_PATH.exists():
+        return True
+    built = FAST_PATH.stat().st_mtime
+    return any(src.stat().st_mtime > built for src in (FAST_SOURCE, HEADERS[-1]))
+
+
+def build_fast(force: bool = False) -> Path:
+    """Compile the CPython binding of ``dxb_wq_gemm_ex`` (gcc, no CUDA involved)."""
+    if not force and not fast_is_stale():
+        return FAST_PATH
+    cc = os.environ.get("CC") or shutil.which("gcc") or shutil.which("cc")
+    if not cc:
+        raise RuntimeError("no C compiler found for csrc/fastcall.c; set CC")
+    cmd = [cc, "-O2", "-shared", "-fPIC", "-I", sysconfig.get_paths()["include"], str(FAST_SOURCE),
+           "-o", str(FAST_PATH)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode:
+        sys.stderr.write(proc.stdout + proc.stderr)
+        raise RuntimeError(f"{cc} failed ({proc.returncode}): {' '.join(cmd)}")
+    return FAST_PATH
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources."""
+    """Compile the library (and the CPython binding of its hot call) if missing or older
+    than the sources."""
+    build_fast(force)
     if not force and not is_stale():
         return LIB_PATH
     cmd = [_nvcc(), *NVCC_FLAGS]

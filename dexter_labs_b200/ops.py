@@ -62,6 +62,7 @@ _opts_cache: Dict[tuple, "_lib.GemmOpts"] = {}  # option structs of calls withou
 # (device, stream) -> (workspace tensor, its address, its size): see _workspace
 _ws_fast: Dict[Tuple[int, int], Tuple[torch.Tensor, int, int]] = {}
 _GEMM = _LIB.dxb_wq_gemm_ex
+_FAST = None if os.environ.get("DEXTER_B200_FASTCALL", "1") == "0" else _lib.load_fast()
 _raw_stream = torch._C._cuda_getCurrentRawStream
 _current_device = torch.cuda.current_device
 
@@ -125,6 +126,20 @@ def _run(bits: int, x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor
     if ws is None or ws[2] < need:
         t = _workspace(x.device, stream, need)
         ws = _ws_fast[(dev, stream)] = (t, t.data_ptr(), t.numel())
+    if reduce is None and _FAST is not None:
+        # compiled binding: same entry point, arguments as plain integers (0 = NULL)
+        rc = _FAST(bits, x2.data_ptr(), x2.stride(0), qweight.data_ptr(), scales.data_ptr(),
+                   0 if zeros is None else zeros.data_ptr(), 0 if bias is None else bias.data_ptr(),
+                   out.data_ptr(), n, m, n, k_dim, group_size, ws[1], ws[2], _LAYOUTS[layout],
+                   _EPILOGUES[epilogue], max_ctas, 1 if copied else 0, stream)
+        if rc != 0:
+            _raise(rc)
+        if _CHECK:
+            code = _LIB.dxb_read_status(ws[1], ctypes.c_void_p(stream))
+            if code != _lib.OK:
+                ws[0].zero_()
+                _raise(code)
+        return out if x.dim() == 2 else out.view(*x.shape[:-1], n)
     if reduce is None:
         okey = (layout, epilogue, max_ctas, copied)
         opts = _opts_cache.get(okey)  # read-only for the library: one struct per combination

@@ -216,6 +216,31 @@ def test_strerror_and_argument_checks(b200_lib):
     assert b200_lib.dxb_uses_tensor_cores(83, 3072, 192, 64, 8) == 0      # int8 with K % 128 != 0
 
 
+def test_compiled_binding_reaches_the_same_entry_point(b200_lib):
+    """`_dxb_fast.gemm` (csrc/fastcall.c) is dxb_wq_gemm_ex with integer arguments: the argument
+    checks answer exactly as through ctypes, before anything touches the device."""
+    from dexter_labs_b200 import _lib
+
+    fast = _lib.load_fast()
+    assert fast is not None, "the compiled binding was not built (dexter_labs_b200/build.py)"
+
+    def call(bits=4, x=16, ldx=256, k=256, group=128):
+        # bits, x, ldx, qweight, scales, zeros, bias, out, ldo, M, N, K, group, ws, ws_bytes,
+        # layout, epilogue, max_ctas, serialize, stream
+        return fast(bits, x, ldx, 16, 16, 0, 0, 16, 16, 1, 16, k, group, 0, 0, 0, 0, 0, 0, 0)
+
+    assert call(bits=5) == -1        # DXB_ERR_BITS
+    assert call(x=0) == -2           # DXB_ERR_NULL
+    assert call(group=96) == -3      # K not a multiple of the group
+    assert call(ldx=128) == -3       # ldx < K
+    with pytest.raises(TypeError):
+        fast(4, 16, 256)
+    with pytest.raises((TypeError, OverflowError)):
+        fast(*(["x"] + [0] * 19))
+    # an unknown layout is refused by the option check, as through ctypes
+    assert fast(4, 16, 256, 16, 16, 0, 0, 16, 16, 1, 16, 256, 128, 0, 0, 7, 0, 0, 0, 0) != 0
+
+
 def test_peer_and_option_entry_points_check_their_arguments(b200_lib):
     """Argument checks of the all-reduce, re-layout and option entry points return before any launch."""
     from dexter_labs_b200 import _lib
