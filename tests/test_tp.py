@@ -99,6 +99,46 @@ def test_row_parallel_sum_matches_unsharded(b200_lib, oracle):
     assert err < 1e-2, err
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_sum_semantics_stay_within_one_bf16_step(world, b200_lib, oracle):
+    """What the sum inside the row-parallel GEMM computes, restated on the CPU: every rank rounds
+    its partial product to bf16, the partials are added in fp32 in rank order, the sum is rounded
+    once and the FULL bias is added after it.  Through a chain of two row-parallel linears (the
+    shape of cross-o -> ffn-up -> ffn-down) the result stays within 1e-2 of the unsharded chain,
+    i.e. one bf16 step at the largest magnitude (0.0079 at the 5B sizes for 2, 4 and 8 ranks)."""
+    from dexter_labs_b200.tp import split_rows
+
+    torch.manual_seed(world)
+    dim, ffn, m = 1024, 2048, 19
+    o_proj = make_weight(dim, dim, 4, 128, True, seed=21)
+    up = make_weight(ffn, dim, 4, 128, True, seed=22)
+    down = make_weight(dim, ffn, 4, 128, True, seed=23)
+    x = torch.randn(m, dim).to(torch.bfloat16)
+
+    def row(inp, full, ranks):
+        if ranks == 1:
+            return oracle_gemm(inp, full)
+        acc = torch.zeros(inp.shape[0], full.qweight.shape[1])
+        for rank in range(ranks):
+            shard, (k0, k1) = split_rows(full, rank, ranks)
+            shard = type(shard)(shard.qweight, shard.scales, shard.zeros, None, shard.group_size, shard.bits,
+                                shard.shape) if shard.bias is not None else shard
+            acc += oracle_gemm(inp[:, k0:k1].contiguous(), shard).float()
+        y = acc.to(torch.bfloat16)
+        return (y.float() + full.bias.float()).to(torch.bfloat16)
+
+    def chain(ranks):
+        h = row(x, o_proj, ranks)
+        h = oracle_gemm(h, up)          # column-parallel: slices along N change nothing
+        return row(h, down, ranks).float()
+
+    want, got = chain(1), chain(world)
+    step = float(want.abs().max()) * 2.0 ** -7   # one bf16 step in the top binade
+    diff = (got - want).abs()
+    assert float(diff.max()) / float(want.abs().max()) < 1e-2
+    assert float(diff.max()) <= 1.01 * step
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
